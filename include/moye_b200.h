@@ -1,0 +1,162 @@
+/*
+ * moye_b200.h -- C ABI of libmoye_b200: the Blackwell (sm_100a) implementation of the tiled
+ * GEMM / TiledCopy hot path of MoYe.jl.
+ *
+ * MoYe.jl itself has no FFI: its `gemm!` / `copyto!` are per-thread device functions that
+ * CUDA.jl compiles into a user kernel (reference examples/gemm.jl:4-64, launched at :86).
+ * The entry points below are what host-level `gemm!(tiled_mma, D, A, B, C)` and
+ * `copyto!(tiled_copy, dst, src)` methods on global-memory MoYeArrays bind to with `ccall`;
+ * every declaration names the reference interface whose work it takes over.
+ *
+ * Conventions
+ *   - All pointers inside a moye_tensor_t are DEVICE pointers owned by the caller, except
+ *     where an entry point says "host".  The library never frees caller memory.
+ *   - Shapes and strides are in ELEMENTS, 0-based arithmetic (offset = sum coord[i]*stride[i]),
+ *     i.e. MoYe's `layout(coord) - 1`.
+ *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*), like the
+ *     `@cuda` launch it replaces.  Return value: 0 on success, a negative moye_status_t
+ *     otherwise; `moye_b200_last_error()` gives a thread-local message.  Nothing aborts,
+ *     traps or throws across this boundary, and there is no CPU fallback.
+ */
+#ifndef MOYE_B200_H
+#define MOYE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOYE_B200_VERSION 100
+#define MOYE_MAX_RANK 4
+#define MOYE_MAX_FLAT_RANK 12
+
+typedef struct moye_b200_ctx* moye_handle_t;
+
+typedef enum {
+  MOYE_OK = 0,
+  MOYE_ERR_INVALID_ARG = -1,
+  MOYE_ERR_UNSUPPORTED_DTYPE = -2,
+  MOYE_ERR_UNSUPPORTED_LAYOUT = -3,
+  MOYE_ERR_UNSUPPORTED_SHAPE = -4,
+  MOYE_ERR_MISALIGNED = -5,
+  MOYE_ERR_CUDA = -6,
+  MOYE_ERR_TIMEOUT = -7,   /* a bounded device-side wait ran out (see moye_b200_status) */
+  MOYE_ERR_NO_DEVICE = -8,
+  MOYE_ERR_TOO_LARGE = -9
+} moye_status_t;
+
+/* Element types.  MoYe spells them Float32, Float16, BFloat16, Int8, UInt8, Int32; e4m3 is
+ * new (the reference has no fp8 type). */
+typedef enum {
+  MOYE_F32 = 0,
+  MOYE_F16 = 1,
+  MOYE_BF16 = 2,
+  MOYE_S8 = 3,
+  MOYE_U8 = 4,
+  MOYE_E4M3 = 5,
+  MOYE_S32 = 6,
+  MOYE_U16 = 7,
+  MOYE_U32 = 8,
+  MOYE_U64 = 9,
+  MOYE_U128 = 10
+} moye_dtype_t;
+
+/* A MoYeArray over global memory, flattened: engine pointer + layout (reference
+ * src/array.jl:53-59 `MoYeArray{T,N,E,L}`, src/engine.jl:6-48 `ViewEngine`). */
+typedef struct {
+  void* ptr;
+  int32_t dtype;                 /* moye_dtype_t */
+  int32_t rank;                  /* 1..MOYE_MAX_RANK */
+  int64_t shape[MOYE_MAX_RANK];
+  int64_t stride[MOYE_MAX_RANK]; /* elements */
+} moye_tensor_t;
+
+/* A flattened Layout (reference src/layout.jl:1-60): `rank` leaf modes in colexicographic
+ * order, as produced by `flatten(layout)`. */
+typedef struct {
+  int32_t rank;                  /* 1..MOYE_MAX_FLAT_RANK */
+  int32_t reserved;
+  int64_t shape[MOYE_MAX_FLAT_RANK];
+  int64_t stride[MOYE_MAX_FLAT_RANK];
+} moye_layout_t;
+
+/* Parameters of the tiled GEMM.  alpha/beta follow `axpby!` (reference
+ * src/algorithm/blas.jl:1-9): D = alpha*scale_a*scale_b*(A.B^T) + beta*C, and C is not read
+ * when beta == 0.  Zero in a tiling field means "library default". */
+typedef struct {
+  float alpha;
+  float beta;
+  float scale_a;                 /* per-tensor dequantisation scales (fp8 path); 1 otherwise */
+  float scale_b;
+  int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128 */
+  int32_t split_k;               /* skinny path only: 0 = auto */
+  int32_t path;                  /* 0 auto, 1 dense persistent kernel, 2 skinny stream-K kernel */
+  int32_t flags;                 /* reserved, must be 0 */
+} moye_gemm_params_t;
+
+typedef enum {
+  MOYE_COPY_AUTO = 0,
+  MOYE_COPY_UNIVERSAL128 = 1,    /* 128-bit UniversalCopy atoms, gmem -> smem -> gmem */
+  MOYE_COPY_TMA = 2              /* cp.async.bulk.tensor load + store through an smem ring */
+} moye_copy_mode_t;
+
+typedef struct {
+  int32_t mode;                  /* moye_copy_mode_t */
+  int32_t tile_m;                /* tile extent along the contiguous mode; 0 = default (128) */
+  int32_t tile_n;                /* tile extent along the strided mode;    0 = default (64)  */
+  int32_t flags;                 /* reserved, must be 0 */
+} moye_copy_params_t;
+
+/* Library lifetime.  A handle is bound to the CUDA device current at creation; it owns a
+ * small device status word, the stream-K workspace and a tensor-map cache.  Replaces nothing
+ * in the reference (CUDA.jl owns the context there). */
+int moye_b200_create(moye_handle_t* out);
+int moye_b200_destroy(moye_handle_t h);
+int moye_b200_version(void);
+const char* moye_b200_last_error(void);
+
+/* Synchronises `stream` and returns the device-side status word: MOYE_OK, or
+ * MOYE_ERR_TIMEOUT if a bounded mbarrier wait inside a kernel gave up (the kernel then tears
+ * down cleanly and the context stays usable).  `site` (may be NULL) receives the code of the
+ * wait that ran out.  The reference's counterpart is `CUDA.synchronize()` after the launch
+ * (reference test/device/matmul.jl:80). */
+int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
+
+/* D = alpha*scale_a*scale_b * A.B^T + beta*C with A:(M,K), B:(N,K), C,D:(M,N).
+ * Takes over the whole `matmul_kernel` of reference examples/gemm.jl:4-64 (the gemm!-based
+ * form is test/device/matmul.jl:3-53): local_tile of A/B/C, the gmem->smem `copyto!`
+ * (src/algorithm/copy.jl:42-64), the `gemm!` tower (src/algorithm/blas.jl:11-131) and the
+ * epilogue `copyto!(gC, rC)` (examples/gemm.jl:62), on tcgen05 tensor cores.
+ * Supported (A,B -> accum -> D): f16,f16 -> f32 -> f32|f16; bf16,bf16 -> f32 -> f32|bf16;
+ * s8,s8 -> s32 -> s32 (bit-exact); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b.
+ * A and B must be K-major (stride 1 along K); D may be M-major or N-major; rows 16-byte
+ * aligned.  C may be NULL when beta == 0.  Violations are errors, never fallbacks. */
+int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t* A,
+                   const moye_tensor_t* B, const moye_tensor_t* C,
+                   const moye_gemm_params_t* params, void* stream);
+
+/* dst = src for two rank-2 tensors of equal shape and dtype whose first mode is contiguous,
+ * tile by tile through shared memory.  Takes over `copy_kernel` (reference
+ * test/host/copy_async.jl:3-25) and `copyto!(tiled_copy, dst, src)` with 128-bit atoms
+ * (src/algorithm/copy.jl:106-130, src/arch/copy/copy.jl:26-51). */
+int moye_b200_copy(moye_handle_t h, const moye_tensor_t* dst, const moye_tensor_t* src,
+                   const moye_copy_params_t* params, void* stream);
+
+/* dst[Ld(i)] = src[Ls(i)] for i in 1:size(Ls), any two layouts of equal size: the
+ * elementwise `copyto!(dst, src)` of reference src/algorithm/copy.jl:4-16,42-64 evaluated
+ * on the device.  elem_bytes in {1,2,4,8,16}. */
+int moye_b200_layout_copy(moye_handle_t h, void* dst, const moye_layout_t* dst_layout,
+                          const void* src, const moye_layout_t* src_layout,
+                          int32_t elem_bytes, void* stream);
+
+/* out[i] = layout(i + first) for i in 0:n-1, with MoYe's 1-based linear indexing
+ * (reference src/layout.jl call operator -> src/stride.jl:20-31 `coord_to_index0`): the
+ * layout function evaluated on the device.  `out` is a device array of n int64. */
+int moye_b200_layout_eval(moye_handle_t h, const moye_layout_t* layout, int64_t first,
+                          int64_t n, int64_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOYE_B200_H */

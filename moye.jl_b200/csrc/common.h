@@ -1,0 +1,102 @@
+// Host-side plumbing shared by the entry points: the handle, error reporting, dtype
+// helpers and tensor-map (TMA descriptor) construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "../../include/moye_b200.h"
+
+namespace moye {
+
+void set_error(const char* fmt, ...);
+const char* get_error();
+
+#define MOYE_FAIL(code, ...)     \
+  do {                           \
+    ::moye::set_error(__VA_ARGS__); \
+    return (code);               \
+  } while (0)
+
+#define MOYE_CUDA(call)                                                                  \
+  do {                                                                                   \
+    cudaError_t e__ = (call);                                                            \
+    if (e__ != cudaSuccess) {                                                            \
+      ::moye::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__); \
+      return MOYE_ERR_CUDA;                                                              \
+    }                                                                                    \
+  } while (0)
+
+inline int dtype_bytes(int dt) {
+  switch (dt) {
+    case MOYE_F32: case MOYE_S32: case MOYE_U32: return 4;
+    case MOYE_F16: case MOYE_BF16: case MOYE_U16: return 2;
+    case MOYE_S8: case MOYE_U8: case MOYE_E4M3: return 1;
+    case MOYE_U64: return 8;
+    case MOYE_U128: return 16;
+    default: return 0;
+  }
+}
+
+struct TmapKey {
+  const void* ptr;
+  int dtype;
+  uint64_t d0, d1, s1;
+  uint32_t b0, b1;
+  int swizzle;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && dtype == o.dtype && d0 == o.d0 && d1 == o.d1 && s1 == o.s1 && b0 == o.b0 &&
+           b1 == o.b1 && swizzle == o.swizzle;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.dtype); mix(k.d0); mix(k.d1); mix(k.s1); mix(k.b0); mix(k.b1); mix(k.swizzle);
+    return h;
+  }
+};
+
+}  // namespace moye
+
+// The handle.  One per (host thread, device).
+struct moye_b200_ctx {
+  int device = -1;
+  int num_sms = 0;
+  int smem_optin = 0;
+  int* d_status = nullptr;          // device status word (0 = OK, else wait-site code)
+  void* workspace = nullptr;        // stream-K partial sums
+  size_t workspace_bytes = 0;
+  std::mutex mu;
+  std::unordered_map<moye::TmapKey, CUtensorMap, moye::TmapKeyHash> tmaps;
+};
+
+namespace moye {
+
+// Encodes (or fetches from the handle's cache) a rank-2 tiled tensor map.
+//   dims  = {extent along the contiguous mode, extent along the strided mode}  (elements)
+//   stride1_bytes = byte stride of the strided mode (multiple of 16)
+//   box   = {box extent contiguous, box extent strided}
+//   swizzle128 = true selects CU_TENSOR_MAP_SWIZZLE_128B (box[0]*elem must be <= 128 bytes)
+int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
+                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);
+
+// Grows the handle-owned workspace to at least `bytes` (never shrinks).
+int ensure_workspace(moye_b200_ctx* h, size_t bytes);
+
+int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                const moye_tensor_t* C, const moye_gemm_params_t* p, cudaStream_t stream);
+int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t* src, const moye_copy_params_t* p,
+                cudaStream_t stream);
+int launch_layout_copy(moye_b200_ctx* h, void* dst, const moye_layout_t* dl, const void* src,
+                       const moye_layout_t* sl, int elem_bytes, cudaStream_t stream);
+int launch_layout_eval(moye_b200_ctx* h, const moye_layout_t* l, int64_t first, int64_t n, int64_t* out,
+                       cudaStream_t stream);
+
+}  // namespace moye

@@ -1,0 +1,332 @@
+// Skinny (decode-shaped) GEMM for sm_100a: D(M,N) = alpha * X(M,K) . W(N,K)^T with M <= 32.
+//
+// The product is bound by reading W once from HBM, so the kernel is organised around keeping
+// as many W bytes in flight as possible:
+//   - operands are swapped for the tensor core: 128 rows of W are the tcgen05 "M" side, the
+//     (zero-padded) rows of X the "N" side, so no MMA lanes are wasted on padding of W;
+//   - stream-K: the (W row-block, K-block) units are dealt out to one persistent CTA per SM in
+//     equal contiguous runs, so every SM streams the same number of bytes whatever N is;
+//   - a 12-deep TMA ring (about 200 KB of loads in flight per SM);
+//   - a CTA whose run covers only part of a row-block's K range writes an fp32 partial to a
+//     workspace; the CTA that arrives last at that row-block (an atomic ticket, no spinning)
+//     sums the partials in CTA order, which makes the result independent of timing.
+//
+// Reference counterpart: the same `matmul_kernel` as the dense path (examples/gemm.jl:4-64);
+// MoYe has no split-K form.  The `gemm!` rank tower it follows is src/algorithm/blas.jl:39-88.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "ptx.cuh"
+
+namespace moye {
+
+struct SkinnyArgs {
+  int M, N, K;
+  int n_tiles, k_blocks;
+  long long units;      // n_tiles * k_blocks
+  uint32_t idesc;
+  float alpha;
+  void* D;
+  long long d_sm, d_sn;  // element strides of D
+  int* tickets;          // [n_tiles], zero between launches
+  float* partials;       // [grid][2][NX][128] fp32
+  int* status;
+};
+
+enum : int { SITE_SK_PROD = 201, SITE_SK_ACC = 202, SITE_SK_FULL = 203, SITE_SK_EPI = 204 };
+
+// AND-reduction of `pred` over the 128 epilogue threads (named barrier 1), so that all four
+// epilogue warps take the same branch after a bounded wait.
+__device__ __forceinline__ bool epi_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, 1, 128, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+__device__ __forceinline__ long long run_start(long long c, long long units, int grid) { return c * units / grid; }
+
+// The CTA whose run contains unit u.
+__device__ __forceinline__ int owner_of(long long u, long long units, int grid) {
+  long long c = u * grid / units;
+  while (c + 1 < grid && run_start(c + 1, units, grid) <= u) ++c;
+  while (c > 0 && run_start(c, units, grid) > u) --c;
+  return (int)c;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_out(void* D, long long off, float f) {
+  if constexpr (sizeof(OutT) == 4) reinterpret_cast<float*>(D)[off] = f;
+  else if constexpr (std::is_same<OutT, __half>::value) reinterpret_cast<__half*>(D)[off] = __float2half_rn(f);
+  else reinterpret_cast<__nv_bfloat16*>(D)[off] = __float2bfloat16_rn(f);
+}
+
+template <typename OutT, int NX, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   const SkinnyArgs g) {
+  constexpr int BK = 64;
+  constexpr int W_BYTES = 128 * 128;
+  constexpr int X_BYTES = NX * 128;
+  constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  constexpr uint32_t TMEM_COLS = (2 * NX < 32) ? 32 : 2 * NX;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  int* ticket_bcast = reinterpret_cast<int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int grid = gridDim.x;
+  const long long u_begin = run_start(blockIdx.x, g.units, grid);
+  const long long u_end = run_start(blockIdx.x + 1, g.units, grid);
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      for (long long u = u_begin; u < u_end; ++u) {
+        const int tile = (int)(u / g.k_blocks);
+        const int kb = (int)(u - (long long)tile * g.k_blocks);
+        if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_SK_PROD)) break;
+        mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+        uint8_t* sw = smem + stage * STAGE_BYTES;
+        tma_load_2d_hint(sw, &tmW, &full[stage], kb * BK, tile * 128, pol_w);
+        tma_load_2d_hint(sw + W_BYTES, &tmX, &full[stage], kb * BK, 0, pol_x);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int seg = 0;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_end && ok) {
+        const int tile = (int)(u / g.k_blocks);
+        const long long tile_end = (long long)(tile + 1) * g.k_blocks;
+        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+        const int buf = seg & 1;
+        const uint32_t aphase = (seg >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE_SK_ACC)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * NX;
+        bool first = true;
+        for (; u < seg_end; ++u) {
+          if (!mbar_wait(&full[stage], phase, g.status, SITE_SK_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sw = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t wdesc = umma_desc_k_sw128(sw);
+          const uint64_t xdesc = umma_desc_k_sw128(sw + W_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tc_mma_ss<KIND_F16>(d_tmem, wdesc + 2 * k, xdesc + 2 * k, g.idesc, (first && k == 0) ? 0u : 1u);
+          }
+          first = false;
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+        ++seg;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    int seg = 0;
+    long long u = u_begin;
+    while (u < u_end) {
+      const int tile = (int)(u / g.k_blocks);
+      const long long tile_begin = (long long)tile * g.k_blocks;
+      const long long tile_end = tile_begin + g.k_blocks;
+      const long long seg_end = tile_end < u_end ? tile_end : u_end;
+      const bool whole = (u == tile_begin) && (seg_end == tile_end);
+      const int buf = seg & 1;
+      const uint32_t aphase = (seg >> 1) & 1;
+      if (!epi_all(mbar_wait(&acc_full[buf], aphase, g.status, SITE_SK_EPI))) break;
+      tc_fence_after_sync();
+      float acc[NX];
+      {
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NX;
+        if constexpr (NX == 16) {
+          uint32_t v[16];
+          tmem_ld_x16(t_addr, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
+        } else {
+          uint32_t v[32];
+          tmem_ld_x32(t_addr, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+
+      const int n_local = q * 32 + lane;
+      const int n = tile * 128 + n_local;
+      if (whole) {
+        if (n < g.N) {
+#pragma unroll
+          for (int m = 0; m < NX; ++m)
+            if (m < g.M) store_out<OutT>(g.D, (long long)m * g.d_sm + (long long)n * g.d_sn, acc[m] * g.alpha);
+        }
+      } else {
+        // partial sum: slot 0 for the first row-block of this CTA's run, slot 1 for the last
+        const int slot = (tile == (int)(u_begin / g.k_blocks)) ? 0 : 1;
+        float* mine = g.partials + ((long long)blockIdx.x * 2 + slot) * (NX * 128);
+#pragma unroll
+        for (int m = 0; m < NX; ++m) __stcg(&mine[m * 128 + n_local], acc[m]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int c_first = owner_of(tile_begin, g.units, grid);
+        const int c_last = owner_of(tile_end - 1, g.units, grid);
+        if (et == 0) {
+          const int old = atomicAdd(&g.tickets[tile], 1);
+          *ticket_bcast = old;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int ticket = *reinterpret_cast<volatile int*>(ticket_bcast);
+        if (ticket == c_last - c_first) {
+          // last to arrive: every partial of this row-block is in memory; sum in CTA order
+          __threadfence();
+          float sum[NX];
+#pragma unroll
+          for (int m = 0; m < NX; ++m) sum[m] = 0.f;
+          for (int c = c_first; c <= c_last; ++c) {
+            const int cslot = (tile == (int)(run_start(c, g.units, grid) / g.k_blocks)) ? 0 : 1;
+            const float* theirs = g.partials + ((long long)c * 2 + cslot) * (NX * 128);
+#pragma unroll
+            for (int m = 0; m < NX; ++m) sum[m] += __ldcg(&theirs[m * 128 + n_local]);
+          }
+          if (n < g.N) {
+#pragma unroll
+            for (int m = 0; m < NX; ++m)
+              if (m < g.M) store_out<OutT>(g.D, (long long)m * g.d_sm + (long long)n * g.d_sn, sum[m] * g.alpha);
+          }
+          if (et == 0) g.tickets[tile] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_bcast may be reused
+      }
+      u = seg_end;
+      ++seg;
+    }
+  }
+
+  if (*reinterpret_cast<volatile int*>(g.status) != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <typename OutT, int NX>
+static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUtensorMap& tx, SkinnyArgs a,
+                              cudaStream_t stream) {
+  constexpr int STAGE = 128 * 128 + NX * 128;
+  constexpr int STAGES = (227 * 1024 - 1024 - 512) / STAGE;
+  constexpr int SMEM = STAGES * STAGE + 512 + 1024;
+  auto kern = gemm_skinny_kernel<OutT, NX, STAGES>;
+  MOYE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  long long grid = h->num_sms;
+  if (grid > a.units) grid = a.units;
+  // workspace: a fixed ticket area (zero at rest: the kernel restores it) then the partial slots
+  constexpr size_t kTicketBytes = 64 * 1024;
+  if ((size_t)a.n_tiles * sizeof(int) > kTicketBytes)
+    MOYE_FAIL(MOYE_ERR_TOO_LARGE, "N = %d exceeds the %zu row-blocks the ticket area holds", a.N,
+              kTicketBytes / sizeof(int));
+  const size_t part_bytes = (size_t)h->num_sms * 2 * NX * 128 * sizeof(float);
+  const size_t need = kTicketBytes + part_bytes;
+  if (need > h->workspace_bytes) {
+    if (int rc = ensure_workspace(h, need)) return rc;
+    MOYE_CUDA(cudaMemsetAsync(h->workspace, 0, kTicketBytes, stream));
+  }
+  a.tickets = reinterpret_cast<int*>(h->workspace);
+  a.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->workspace) + kTicketBytes);
+  kern<<<(int)grid, 192, SMEM, stream>>>(tw, tx, a);
+  MOYE_CUDA(cudaGetLastError());
+  return MOYE_OK;
+}
+
+int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                       const moye_gemm_params_t* p, cudaStream_t stream) {
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (A->dtype != MOYE_F16 && A->dtype != MOYE_BF16)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "the skinny path takes f16 or bf16 operands");
+  if (M > 32) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "the skinny path needs M <= 32 (got %lld)", (long long)M);
+  if (p->beta != 0.f) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the skinny path does not read C (beta must be 0)");
+  const int out = D->dtype;
+  if (!(out == MOYE_F32 || (out == MOYE_F16 && A->dtype == MOYE_F16) || (out == MOYE_BF16 && A->dtype == MOYE_BF16)))
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
+  const int nx = M <= 16 ? 16 : 32;
+  CUtensorMap tw, tx;
+  if (int rc = make_tmap_2d(h, &tw, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * 2, 64, 128, true)) return rc;
+  if (int rc = make_tmap_2d(h, &tx, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * 2, 64, nx, true)) return rc;
+  SkinnyArgs a;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K;
+  a.n_tiles = (int)((N + 127) / 128);
+  a.k_blocks = (int)((K + 63) / 64);
+  a.units = (long long)a.n_tiles * a.k_blocks;
+  const uint32_t fmt = A->dtype == MOYE_BF16 ? 1u : 0u;
+  a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(nx >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  a.alpha = p->alpha * p->scale_a * p->scale_b;
+  a.D = D->ptr;
+  a.d_sm = D->stride[0];
+  a.d_sn = D->stride[1];
+  a.partials = nullptr;
+  a.tickets = nullptr;
+  a.status = h->d_status;
+  if (nx == 16) {
+    if (out == MOYE_F32) return launch_skinny_inst<float, 16>(h, tw, tx, a, stream);
+    if (out == MOYE_F16) return launch_skinny_inst<__half, 16>(h, tw, tx, a, stream);
+    return launch_skinny_inst<__nv_bfloat16, 16>(h, tw, tx, a, stream);
+  } else {
+    if (out == MOYE_F32) return launch_skinny_inst<float, 32>(h, tw, tx, a, stream);
+    if (out == MOYE_F16) return launch_skinny_inst<__half, 32>(h, tw, tx, a, stream);
+    return launch_skinny_inst<__nv_bfloat16, 32>(h, tw, tx, a, stream);
+  }
+}
+
+}  // namespace moye

@@ -1,0 +1,425 @@
+// Dense tiled GEMM for sm_100a: D = alpha * A.B^T (+ beta*C), A:(M,K) and B:(N,K) K-major.
+//
+// This kernel is the Blackwell re-design of MoYe's `matmul_kernel` (reference
+// examples/gemm.jl:4-64).  The roles of the reference's steps map as follows:
+//   @tile mA (bM,bK) (blockIdx.x, :)           -> TMA tensor-map box + tile coordinates
+//   copyto!(sA, gA) ; cp_async_wait ; sync     -> cp.async.bulk.tensor into a 128B-swizzled
+//                                                 smem ring, mbarrier full/empty pipeline
+//   gemm!(rC, sA, sB, rC) / FMA triple loop    -> tcgen05.mma, accumulator in tensor memory
+//   copyto!(gC, rC)                            -> tcgen05.ld -> registers -> smem -> TMA store
+//
+// One persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer (also owns
+// the TMEM allocation), warps 2-5 = epilogue.  The accumulator is double-buffered in TMEM
+// so the epilogue of tile i overlaps the main loop of tile i+1.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "ptx.cuh"
+
+namespace moye {
+
+struct GemmArgs {
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  int group_m;
+  uint32_t idesc;
+  float alpha;  // alpha * scale_a * scale_b
+  float beta;
+  const void* C;
+  long long c_sm, c_sn;  // strides of C in elements
+  int* status;
+};
+
+// Wait-site codes reported through the status word.
+enum : int { SITE_PROD_EMPTY = 101, SITE_MMA_ACC = 102, SITE_MMA_FULL = 103, SITE_EPI_ACC = 104 };
+
+__device__ __forceinline__ void tile_coord(int t, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+  // Grouped raster: tiles that run concurrently cover `group_m` row-blocks x a few
+  // column-blocks, so their A and B panels are shared through L2.
+  const int per_group = group_m * n_tiles;
+  const int grp = t / per_group;
+  const int first_m = grp * group_m;
+  const int gsz = min(group_m, m_tiles - first_m);
+  const int r = t - grp * per_group;
+  mi = first_m + r % gsz;
+  ni = r / gsz;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT cvt_out(float f);
+template <>
+__device__ __forceinline__ float cvt_out<float>(float f) { return f; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+template <>
+__device__ __forceinline__ __half cvt_out<__half>(float f) { return __float2half_rn(f); }
+
+template <typename OutT>
+__device__ __forceinline__ float load_c_as_float(const void* C, long long off) {
+  return static_cast<float>(reinterpret_cast<const OutT*>(C)[off]);
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+  constexpr int BM = 128;
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int BK = 128 / ELEM;       // one 128-byte swizzle row of K per stage
+  constexpr int UMMA_K = 32 / ELEM;    // K of one tcgen05.mma
+  constexpr int A_BYTES = BM * 128;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int EPI_BUF = 4096;        // one staging buffer of one epilogue warp
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr bool INT_OUT = (KIND == KIND_I8);
+  static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile N");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + 8 * EPI_BUF);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = g.m_tiles * g.n_tiles;
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mi, ni;
+        tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_PROD_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          tma_load_2d(sa, &tmA, &full[stage], kb * BK, mi * BM);
+          tma_load_2d(sa + A_BYTES, &tmB, &full[stage], kb * BK, ni * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int lt = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+        const int buf = lt & 1;
+        const uint32_t aphase = (lt >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE_MMA_ACC)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, g.status, SITE_MMA_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k_sw128(sa);
+          const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by one instruction = 32 bytes inside the swizzled row = +2 in the
+            // (address >> 4) field of the descriptor
+            tc_mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // the TMEM lane quarter this warp may read
+    uint8_t* my_buf = epi + (warp - 2) * 2 * EPI_BUF;
+    int nstore = 0;
+    int lt = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++lt) {
+      int mi, ni;
+      tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+      const int buf = lt & 1;
+      const uint32_t aphase = (lt >> 1) & 1;
+      if (!mbar_wait(&acc_full[buf], aphase, g.status, SITE_EPI_ACC)) break;
+      tc_fence_after_sync();
+      const int m0 = mi * BM + q * 32;
+      const int n0 = ni * BN;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+
+      // columns handled per TMA store: a 128-byte row for N-major output, 32 for M-major
+      constexpr int SC = OUT_M_MAJOR ? 32 : (128 / (int)sizeof(OutT));
+      constexpr int SUB = SC / 32;
+#pragma unroll 1
+      for (int c = 0; c < BN / SC; ++c) {
+        uint8_t* sb = my_buf + (nstore & 1) * EPI_BUF;
+        if (lane == 0) tma_store_wait_read<1>();  // the store that last used `sb` has drained
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) {
+          uint32_t v[32];
+          const int col0 = c * SC + s * 32;
+          tmem_ld_x32(t_addr + col0, v);
+          tmem_ld_wait();
+          if (c == BN / SC - 1 && s == SUB - 1) {
+            // last read of this accumulator: hand it back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          if (g.beta != 0.f) {
+            const int row = m0 + lane;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = n0 + col0 + j;
+              if (row < g.M && col < g.N) {
+                const long long off = (long long)row * g.c_sm + (long long)col * g.c_sn;
+                if constexpr (INT_OUT) {
+                  v[j] = (uint32_t)((int)v[j] + reinterpret_cast<const int*>(g.C)[off]);
+                } else {
+                  float cin = load_c_as_float<OutT>(g.C, off);
+                  v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha + g.beta * cin);
+                }
+              }
+            }
+          } else if constexpr (!INT_OUT) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha);
+          }
+          if constexpr (OUT_M_MAJOR) {
+            // staging tile is [32 columns][32 rows], rows contiguous: conflict-free
+            if constexpr (INT_OUT) {
+              int* so = reinterpret_cast<int*>(sb);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) so[j * 32 + lane] = (int)v[j];
+            } else {
+              OutT* so = reinterpret_cast<OutT*>(sb);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) so[j * 32 + lane] = cvt_out<OutT>(__uint_as_float(v[j]));
+            }
+          } else {
+            // staging tile is [32 rows][128 bytes] in the 128-byte swizzle the store map expects
+            uint8_t* rowp = sb + lane * 128;
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  OutT lo = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e]));
+                  OutT hi = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e + 1]));
+                  w[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) |
+                         ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                }
+                const int chunk = s * 4 + j;
+                *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (OUT_M_MAJOR)
+            tma_store_2d(&tmD, sb, m0, n0 + c * SC);
+          else
+            tma_store_2d(&tmD, sb, n0 + c * SC, m0);
+          tma_store_commit();
+        }
+        ++nstore;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*reinterpret_cast<volatile int*>(g.status) != 0) {
+    // A wait gave up somewhere: give copies still in flight time to land before the CTA
+    // (and its shared memory) goes away.
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------- host side
+
+template <int BN>
+constexpr int stages_for() {
+  return (227 * 1024 - 8 * 4096 - 1024 - 256) / (128 * 128 + BN * 128);
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN>
+static int launch_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                       const GemmArgs& args, cudaStream_t stream) {
+  constexpr int STAGES = stages_for<BN>();
+  static_assert(STAGES >= 3, "pipeline too shallow");
+  constexpr int SMEM = STAGES * (128 * 128 + BN * 128) + 8 * 4096 + 256 + 1024;
+  auto kern = gemm_tcgen05_kernel<KIND, OutT, OUT_M_MAJOR, BN, STAGES>;
+  MOYE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  const int tiles = args.m_tiles * args.n_tiles;
+  const int grid = tiles < h->num_sms ? tiles : h->num_sms;
+  kern<<<grid, 192, SMEM, stream>>>(ta, tb, td, args);
+  MOYE_CUDA(cudaGetLastError());
+  return MOYE_OK;
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR>
+static int launch_bn(int bn, moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                     const GemmArgs& args, cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_inst<KIND, OutT, OUT_M_MAJOR, 256>(h, ta, tb, td, args, stream);
+    case 128: return launch_inst<KIND, OutT, OUT_M_MAJOR, 128>(h, ta, tb, td, args, stream);
+    case 64: return launch_inst<KIND, OutT, OUT_M_MAJOR, 64>(h, ta, tb, td, args, stream);
+    default: MOYE_FAIL(MOYE_ERR_INVALID_ARG, "tile_n must be 64, 128 or 256 (got %d)", bn);
+  }
+}
+
+template <int KIND, typename OutT>
+static int launch_major(bool m_major, int bn, moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb,
+                        const CUtensorMap& td, const GemmArgs& args, cudaStream_t stream) {
+  return m_major ? launch_bn<KIND, OutT, true>(bn, h, ta, tb, td, args, stream)
+                 : launch_bn<KIND, OutT, false>(bn, h, ta, tb, td, args, stream);
+}
+
+int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                       const moye_gemm_params_t* p, cudaStream_t stream);
+
+int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                const moye_tensor_t* C, const moye_gemm_params_t* pp, cudaStream_t stream) {
+  moye_gemm_params_t p = {1.f, 0.f, 1.f, 1.f, 0, 0, 0, 0};
+  if (pp) p = *pp;
+  if (p.flags != 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "flags must be 0");
+  if (A->rank != 2 || B->rank != 2 || D->rank != 2) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "A, B, D must be rank 2");
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (B->shape[1] != K || D->shape[0] != M || D->shape[1] != N)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "shape mismatch: A (%lld,%lld) B (%lld,%lld) D (%lld,%lld)", (long long)M,
+              (long long)K, (long long)N, (long long)B->shape[1], (long long)D->shape[0], (long long)D->shape[1]);
+  if (M <= 0 || N <= 0 || K <= 0) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "empty GEMM");
+  if (M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2) MOYE_FAIL(MOYE_ERR_TOO_LARGE, "extent too large");
+  if (!A->ptr || !B->ptr || !D->ptr) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "null data pointer");
+  if (A->dtype != B->dtype) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "A and B must have the same dtype");
+
+  int kind;
+  uint32_t ab_fmt, c_fmt;
+  switch (A->dtype) {
+    case MOYE_F16: kind = KIND_F16; ab_fmt = 0; c_fmt = 1; break;
+    case MOYE_BF16: kind = KIND_F16; ab_fmt = 1; c_fmt = 1; break;
+    case MOYE_S8: kind = KIND_I8; ab_fmt = 1; c_fmt = 2; break;
+    case MOYE_E4M3: kind = KIND_F8; ab_fmt = 0; c_fmt = 1; break;
+    default: MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "operand dtype %d is not supported by the tcgen05 path", A->dtype);
+  }
+  const int out = D->dtype;
+  const bool out_ok = (A->dtype == MOYE_F16 && (out == MOYE_F32 || out == MOYE_F16)) ||
+                      (A->dtype == MOYE_BF16 && (out == MOYE_F32 || out == MOYE_BF16)) ||
+                      (A->dtype == MOYE_S8 && out == MOYE_S32) ||
+                      (A->dtype == MOYE_E4M3 && (out == MOYE_BF16 || out == MOYE_F32));
+  if (!out_ok) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
+  if (A->stride[1] != 1 || B->stride[1] != 1)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B must be K-major (stride 1 along K); got %lld and %lld",
+              (long long)A->stride[1], (long long)B->stride[1]);
+  bool m_major;
+  if (D->stride[0] == 1 && (D->stride[1] != 1 || N == 1)) m_major = true;
+  else if (D->stride[1] == 1) m_major = false;
+  else MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "D must have a unit stride in one mode");
+
+  float alpha = p.alpha * p.scale_a * p.scale_b;
+  if (kind == KIND_I8) {
+    if (alpha != 1.f || (p.beta != 0.f && p.beta != 1.f))
+      MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the s8 -> s32 path is exact integer arithmetic: alpha must be 1, beta 0 or 1");
+  }
+  if (p.beta != 0.f) {
+    if (!C || !C->ptr) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "beta != 0 needs C");
+    if (C->rank != 2 || C->shape[0] != M || C->shape[1] != N || C->dtype != D->dtype)
+      MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "C must match D in shape and dtype");
+  }
+
+  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512))
+    return launch_gemm_skinny(h, D, A, B, &p, stream);
+
+  int bn = p.tile_n;
+  if (bn == 0) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+
+  const int eb = dtype_bytes(A->dtype);
+  const int bk = 128 / eb;
+  CUtensorMap ta, tb, td;
+  if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * eb, bk, 128, true)) return rc;
+  if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, bn, true)) return rc;
+  const int ob = dtype_bytes(out);
+  if (m_major) {
+    if (int rc = make_tmap_2d(h, &td, D->ptr, out, M, N, (uint64_t)D->stride[1] * ob, 32, 32, false)) return rc;
+  } else {
+    if (int rc = make_tmap_2d(h, &td, D->ptr, out, N, M, (uint64_t)D->stride[0] * ob, 128 / ob, 32, true)) return rc;
+  }
+
+  GemmArgs a;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K;
+  a.m_tiles = (int)((M + 127) / 128);
+  a.n_tiles = (int)((N + bn - 1) / bn);
+  a.k_blocks = (int)((K + bk - 1) / bk);
+  a.group_m = 16;
+  a.idesc = (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  a.alpha = alpha;
+  a.beta = p.beta;
+  a.C = (p.beta != 0.f) ? C->ptr : nullptr;
+  a.c_sm = (p.beta != 0.f) ? C->stride[0] : 0;
+  a.c_sn = (p.beta != 0.f) ? C->stride[1] : 0;
+  a.status = h->d_status;
+
+  if (kind == KIND_F16) {
+    if (out == MOYE_F32) return launch_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);
+    if (out == MOYE_F16) return launch_major<KIND_F16, __half>(m_major, bn, h, ta, tb, td, a, stream);
+    return launch_major<KIND_F16, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+  } else if (kind == KIND_I8) {
+    return launch_major<KIND_I8, int>(m_major, bn, h, ta, tb, td, a, stream);
+  } else {
+    if (out == MOYE_F32) return launch_major<KIND_F8, float>(m_major, bn, h, ta, tb, td, a, stream);
+    return launch_major<KIND_F8, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+  }
+}
+
+}  // namespace moye
