@@ -1,0 +1,180 @@
+"""`copyto_` and `gemm_`: MoYe's L5 algorithms (`copyto!`, `gemm!`) at host level.
+
+In MoYe these are per-thread device functions inlined into a user kernel (reference
+src/algorithm/copy.jl, src/algorithm/blas.jl).  Here the same calls, made on arrays that live
+in global memory, hand the whole tiled operation to libmoye_b200 through its C ABI:
+
+    copyto_(tiled_copy, dst, src)   ->  moye_b200_copy         (reference copy.jl:106-130)
+    copyto_(dst, src)               ->  moye_b200_copy or moye_b200_layout_copy (copy.jl:42-64)
+    gemm_(tiled_mma, D, A, B, C)    ->  moye_b200_gemm         (reference blas.jl:11-131)
+    matmul(A, B, C)                 ->  the `matmul` of examples/gemm.jl:66-89
+
+There is no CPU implementation behind these names: operands in host memory are rejected.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from .array import MoYeArray, isgmem
+from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
+from .layout import Layout, coalesce, size
+
+__all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr"]
+
+
+def current_stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _need_gmem(*arrays):
+    for x in arrays:
+        if not isgmem(x):
+            raise RuntimeError("libmoye_b200 runs on device global memory only; got an array on "
+                               f"{x.device} (there is no CPU fallback)")
+    dev = arrays[0].device
+    for x in arrays[1:]:
+        if x.device != dev:
+            raise RuntimeError("operands live on different devices")
+    return dev
+
+
+def _as_rank2(x):
+    """(shape, stride) of a rank-2 view whose modes are single strides, or None."""
+    l = x.layout
+    if len(l) != 2:
+        return None
+    modes = [coalesce(l[0]), coalesce(l[1])]
+    if any(isinstance(m.shape, tuple) for m in modes):
+        return None
+    return [int(m.shape) for m in modes], [int(m.stride) for m in modes]
+
+
+def _tensor_arg(x, what):
+    sd = _as_rank2(x)
+    if sd is None:
+        raise _lib.MoyeError(-3, f"{what} must be a rank-2 array with one stride per mode, got layout {x.layout}")
+    return _lib.make_tensor(x.ptr, x.dtype, sd[0], sd[1])
+
+
+def copyto_(*args, stream=None):
+    """`copyto!(dst, src)` or `copyto!(tiled_copy, dst, src)` on global-memory arrays."""
+    if len(args) == 3:
+        tiled_copy, dst, src = args
+    else:
+        (dst, src), tiled_copy = args, None
+    dev = _need_gmem(dst, src)
+    lib, h = _lib.load(), _lib.handle(dev.index)
+    st = stream if stream is not None else current_stream_ptr(dev)
+    if size(dst.layout) != size(src.layout):
+        raise _lib.MoyeError(-4, f"copyto!: sizes differ ({size(dst.layout)} vs {size(src.layout)})")
+    if dst.storage.dtype != src.storage.dtype:
+        raise _lib.MoyeError(-2, "copyto!: element types differ")
+    if size(src.layout) == 0:
+        return dst
+    params = None
+    if tiled_copy is not None:
+        if not isinstance(tiled_copy, TiledCopy):
+            raise TypeError("first argument must be a TiledCopy")
+        mode = tiled_copy.copy_atom.op.mode
+        if mode is None:
+            raise _lib.MoyeError(-3, f"{tiled_copy.copy_atom.op} is narrower than 128 bits; the device copy kernels "
+                                     "move 128-bit atoms or TMA tiles")
+        tm, tn = tiled_copy.tiler_mn[0], tiled_copy.tiler_mn[1] if len(tiled_copy.tiler_mn) > 1 else 1
+        if mode == _lib.COPY_UNIVERSAL128:
+            # the tiler of one pass is (threads x vector) wide; the kernel loops it over a CTA tile of
+            # 64 columns like the reference's copy kernel loops its partition
+            tn = max(tn, 64)
+        params = _lib.CopyParams(mode, tm, tn, 0)
+    sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
+    tiled_ok = (sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0] and sd_d[1][0] == 1 and sd_s[1][0] == 1)
+    if tiled_ok:
+        td = _lib.make_tensor(dst.ptr, dst.dtype, sd_d[0], sd_d[1])
+        ts = _lib.make_tensor(src.ptr, src.dtype, sd_s[0], sd_s[1])
+        rc = lib.moye_b200_copy(h, ctypes.byref(td), ctypes.byref(ts), ctypes.byref(params) if params else None, st)
+        if rc == 0:
+            return dst
+        if tiled_copy is not None or rc not in (-5, -3):
+            _lib.check(rc)
+    elif tiled_copy is not None:
+        raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode")
+    # elementwise through both layouts
+    ds, dd = dst.layout.flat()
+    ss, sdd = src.layout.flat()
+    if len(ds) > _lib.MAX_FLAT_RANK or len(ss) > _lib.MAX_FLAT_RANK:
+        raise _lib.MoyeError(-4, "layout has too many modes")
+    ld, ls = _lib.make_flat_layout(ds, dd), _lib.make_flat_layout(ss, sdd)
+    _lib.check(lib.moye_b200_layout_copy(h, ctypes.c_void_p(dst.ptr), ctypes.byref(ld), ctypes.c_void_p(src.ptr),
+                                         ctypes.byref(ls), dst.elem_bytes, st))
+    return dst
+
+
+_AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.E4M3: "E4M3"}
+
+
+def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None):
+    """`gemm!([tiled_mma,] D, A, B, C)`: D = alpha*scale_a*scale_b * A.B^T + beta*C with
+    A:(M,K), B:(N,K), C and D:(M,N) in global memory.  `gemm_(A, B, C)` is `gemm!(C, A, B, C)`
+    like the reference's three-argument form (src/algorithm/blas.jl:11)."""
+    tiled_mma = None
+    if args and isinstance(args[0], TiledMMA):
+        tiled_mma, args = args[0], args[1:]
+    if len(args) == 3:
+        A, B, C = args
+        D = C
+    elif len(args) == 4:
+        D, A, B, C = args
+    else:
+        raise TypeError("gemm_([tiled_mma,] D, A, B, C) or gemm_([tiled_mma,] A, B, C)")
+    ops = [D, A, B] + ([C] if (C is not None and beta != 0.0) else [])
+    dev = _need_gmem(*ops)
+    if tiled_mma is not None:
+        op = tiled_mma.atom.op
+        if op.arch != "sm_100a":
+            raise _lib.MoyeError(-2, f"{op} is not a tcgen05 op; device-level gemm! needs an MMAOP_SM100_* atom")
+        if op.valtype_a != A.dtype or op.valtype_b != B.dtype:
+            raise _lib.MoyeError(-2, f"{op} does not take these operand types")
+        if tile_n == 0:
+            tile_n = tiled_mma.tile_size(1)
+    lib, h = _lib.load(), _lib.handle(dev.index)
+    st = stream if stream is not None else current_stream_ptr(dev)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, 0)
+    tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
+    tC = _tensor_arg(C, "C") if (C is not None and beta != 0.0) else None
+    _lib.check(lib.moye_b200_gemm(h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB),
+                                  ctypes.byref(tC) if tC is not None else None, ctypes.byref(p), st))
+    return D
+
+
+def matmul(A, B, C, **kw):
+    """`matmul(A, B, C)` of reference examples/gemm.jl:66-89: C = A * B' for device arrays,
+    with the tcgen05 atom chosen from the operand type.  Accepts MoYeArrays or torch tensors
+    (a torch (rows, cols) tensor is taken with its own strides)."""
+    A, B, C = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (A, B, C))
+    if A.dtype not in _AB_TAG:
+        raise _lib.MoyeError(-2, "matmul takes f16, bf16, s8 or e4m3 operands on sm_100a")
+    n = C.layout.shape[1]
+    mma = make_tiled_mma(sm100_mma_op(_AB_TAG[A.dtype], 256 if n > 128 else (128 if n > 64 else 64)))
+    return gemm_(mma, C, A, B, None, **kw)
+
+
+def layout_eval(layout, n=None, first=1, device=None, stream=None):
+    """Evaluate `layout(first), ..., layout(first+n-1)` on the device; returns an int64 tensor."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    n = size(layout) if n is None else n
+    fs, fd = layout.flat()
+    fl = _lib.make_flat_layout(fs, fd)
+    out = torch.empty(n, dtype=torch.int64, device=device)
+    lib, h = _lib.load(), _lib.handle(device.index)
+    st = stream if stream is not None else current_stream_ptr(device)
+    _lib.check(lib.moye_b200_layout_eval(h, ctypes.byref(fl), first, n, ctypes.c_void_p(out.data_ptr()), st))
+    return out
+
+
+def synchronize_status(device=None, stream=None):
+    """Synchronise the stream and raise if a device-side bounded wait gave up."""
+    device = torch.cuda.current_device() if device is None else torch.device(device).index
+    lib, h = _lib.load(), _lib.handle(device)
+    st = stream if stream is not None else current_stream_ptr(device)
+    site = ctypes.c_int32(0)
+    _lib.check(lib.moye_b200_status(h, st, ctypes.byref(site)))

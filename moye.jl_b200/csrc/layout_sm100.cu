@@ -3,6 +3,7 @@
 // A MoYe `Layout` maps a 1-based linear index to a 1-based offset:
 //   layout(i) = 1 + sum_k ((i-1) / prod(shape[0..k-1]) % shape[k]) * stride[k]
 // over the flattened modes in colexicographic order; the last mode wraps like the others
+// and a layout with a single mode does not wrap at all
 // (reference src/stride.jl:20-31 `coord_to_index0` applied to an integer coordinate, reached
 // from the call operator in src/layout.jl).  `copyto!(dst, src)` walks i = 1:size(src) through
 // both layouts (reference src/algorithm/copy.jl:4-16,42-64).
@@ -17,6 +18,7 @@ struct FlatLayout {
 };
 
 __device__ __forceinline__ long long layout_offset0(const FlatLayout& l, long long idx0) {
+  if (l.rank == 1) return idx0 * l.stride[0];  // a single mode does not wrap
   long long off = 0;
 #pragma unroll 1
   for (int k = 0; k < l.rank; ++k) {
