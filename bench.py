@@ -1,0 +1,468 @@
+"""Benchmark of the hot path: the tiled GEMM of MoYe's examples/gemm.jl on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input.  The default
+workload is the dense fp16 x fp16 -> fp32 GEMM with M = N = K = 8192 (K-major A and B,
+U[-1,1) entries, alpha = 1, beta = 0).  With N GPUs every rank owns one M-shard of a global
+(N*8192) x 8192 x 8192 product with B replicated, so per-GPU work is fixed (weak scaling) and
+there is no collective in the timed region.
+
+Rank 0 prints ONE JSON line.  `value` is whole-job TFLOP/s with the operands resident in HBM
+(CUDA events on the launching stream, max over ranks); `e2e` is the same product through the
+package's public call with pinned HOST buffers, host<->device copies inside the timed region;
+`roofline` compares the kernel with the measured cuBLAS bf16 peak of this pool;
+`cpu_baseline` times the CPU restatement of the reference's host path on a bounded sample.
+
+`--impl reference` times only the reference's host implementation (the CPU restatement under
+oracle/, all host threads) on bounded samples of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM traffic of one launch of the 8192^3 fp16 GEMM kernel (dram__bytes_read.sum +
+# dram__bytes_write.sum from the ncu capture summarised under profiles/); None until captured.
+NCU_TRAFFIC_BYTES = {"gemm_f16_8192": None}
+
+WORKLOADS = {
+    # name: (kind, M, N, K, out)
+    "gemm_f16_8192": ("f16", 8192, 8192, 8192, "f32"),
+    "gemm_f16_4096": ("f16", 4096, 4096, 4096, "f32"),
+    "gemm_bf16_8192": ("bf16", 8192, 8192, 8192, "f32"),
+    "gemm_s8_16384x8192x8192": ("s8", 16384, 8192, 8192, "s32"),
+    "gemm_e4m3_16384x8192x8192": ("e4m3", 16384, 8192, 8192, "bf16"),
+    "decode_bf16_16x28672x8192": ("bf16", 16, 28672, 8192, "bf16"),
+    "copy_f16_8192": ("copy", 8192, 8192, 0, "f16"),
+    # a smaller case of the same dense kernel (224 MB of operands + output, still larger than L2),
+    # sized for multi-pass profiler captures
+    "gemm_f16_4096x8192x4096": ("f16", 4096, 8192, 4096, "f32"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+
+    REASONS = {0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x8: "hw_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+               0x10: "sync_boost"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for b, name in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "samples": len(s),
+                "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------- helpers
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def flops_of(kind, M, N, K):
+    return 2.0 * M * N * K
+
+
+def make_operands(torch, kind, M, N, K, out, dev, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    if kind == "f16":
+        A = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).half()
+        B = (torch.rand(N, K, device=dev, generator=g) * 2 - 1).half()
+    elif kind == "bf16":
+        A = (torch.randn(M, K, device=dev, generator=g) * 0.02).bfloat16()
+        B = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
+    elif kind == "s8":
+        A = torch.randint(-128, 128, (M, K), device=dev, generator=g, dtype=torch.int8)
+        B = torch.randint(-128, 128, (N, K), device=dev, generator=g, dtype=torch.int8)
+    else:
+        A = torch.randn(M, K, device=dev, generator=g).clamp(-448, 448).to(torch.float8_e4m3fn)
+        B = torch.randn(N, K, device=dev, generator=g).clamp(-448, 448).to(torch.float8_e4m3fn)
+    odt = {"f32": torch.float32, "s32": torch.int32, "bf16": torch.bfloat16, "f16": torch.float16}[out]
+    C = torch.zeros(M, N, device=dev, dtype=odt)
+    return A, B, C
+
+
+def time_launches(torch, fn, steps, warmup, stream):
+    """Average device time of `fn` in ms: CUDA events on the launching stream, sync on both sides."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_reference_rate(ho, np, M, N, K, seconds, threads):
+    """Times the threaded host GEMM of the reference (restated in oracle/moye_host.c after
+    test/host/tiling_matmul.jl:20-39) on the first rows of C of an (M,N,K) fp32 problem.
+    Returns (TFLOP/s, rows, elapsed seconds, thread layout)."""
+    tr = 1
+    while tr * tr * 4 <= threads:
+        tr *= 2
+    tc = max(1, threads // tr)
+    A = ho.uniform_pm1(3, (M * K,))
+    B = ho.uniform_pm1(4, (N * K,))
+    probe_rows = tr
+    t0 = time.perf_counter()
+    ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc), m_limit=probe_rows)
+    dt = max(time.perf_counter() - t0, 1e-6)
+    rate = 2.0 * probe_rows * N * K / dt
+    rows = int(max(tr, min(M, (seconds * rate / (2.0 * N * K)) // tr * tr)))
+    t0 = time.perf_counter()
+    ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc), m_limit=rows)
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * N * K / dt / 1e12, rows, dt, (tr, tc)
+
+
+def run_reference_arm(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return 0
+    import numpy as np
+    import __graft_entry__ as ge
+    ho, _ = ge.load_oracle()
+    ho.lib()
+    kind, M, N, K, out = WORKLOADS[args.workload]
+    if kind == "copy":
+        raise SystemExit("the reference arm times the GEMM workloads")
+    threads = os.cpu_count() or 1
+    total = args.steps + args.warmup
+    per_step = min(5.0, max(0.2, 75.0 / max(1, total)))
+    tr = 1
+    while tr * tr * 4 <= threads:
+        tr *= 2
+    tc = max(1, threads // tr)
+    A = ho.uniform_pm1(3, (M * K,))
+    B = ho.uniform_pm1(4, (N * K,))
+    t0 = time.perf_counter()
+    ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc), m_limit=tr)
+    rate = 2.0 * tr * N * K / max(time.perf_counter() - t0, 1e-6)
+    rows = int(max(tr, min(M, (per_step * rate / (2.0 * N * K)) // tr * tr)))
+    for _ in range(args.warmup):
+        ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc), m_limit=rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc), m_limit=rows)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = 2.0 * rows * N * K / dt / 1e12
+    sample = f"first {rows} of {M} rows of C per step, N={N}, K={K}, fp32 (inputs widened), thread layout ({tr},{tc})"
+    line = {
+        "impl": "reference", "metric": "GEMM TFLOP/s", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, args.gpus),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": tr * tc, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "MoYe.jl is Julia and cannot run here; this is the C restatement of its threaded host gemm "
+                "(oracle/moye_host.c), throughput measured on a row sample, not extrapolated in time",
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(name, gpus):
+    kind, M, N, K, out = WORKLOADS[name]
+    return {"workload": name, "M_per_gpu": M, "N": N, "K": K, "global_M": M * gpus, "layout": "A,B K-major (TN); D row-major",
+            "in": kind, "out": out, "sharding": f"M-sharded x{gpus}, B replicated, no collective",
+            "l2": "operands+output exceed the 126 MB L2 (no flush needed)" if M * K + N * K > 64e6 else "rotating buffers"}
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import __graft_entry__ as ge
+
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000), __file__] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    mb = ge.load_package()
+    peaks, peak_src = measured_peaks()
+    stream = torch.cuda.current_stream()
+    name = args.workload
+    kind, M, N, K, out = WORKLOADS[name]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if kind == "copy":
+        return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier)
+
+    A, B, C = make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank)
+    kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
+    mA, mB, mC = mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(C)
+
+    def step():
+        mb.matmul(mA, mB, mC, **kw)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    mb.synchronize_status(dev)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    mb.synchronize_status(dev)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    total_flops = flops_of(kind, M, N, K) * world
+    value = total_flops / (ms_max * 1e-3) / 1e12
+    bytes_bound = kind == "bf16" and M <= 32
+
+    # end to end: pinned host operands -> device -> GEMM -> host, every step
+    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
+    hC = torch.empty(C.shape, dtype=C.dtype).pin_memory()
+    e2e_steps = max(1, min(args.steps, 10))
+
+    def e2e_step():
+        A.copy_(hA, non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        mb.matmul(mA, mB, mC, **kw)
+        hC.copy_(C, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    h2d = A.numel() * A.element_size() + B.numel() * B.element_size()
+    d2h = C.numel() * C.element_size()
+
+    if bytes_bound:
+        alg_bytes = h2d + d2h
+        achieved, peak, unit, bound = alg_bytes / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
+        metric, munit = "decode GEMM GB/s", "GB/s"
+        value = alg_bytes * world / (ms_max * 1e-3) / 1e9
+        e2e_val = alg_bytes * world / (e2e_ms * 1e-3) / 1e9
+        peak_kind = "hbm copy"
+    else:
+        long_run = ms * args.steps > 1000.0
+        peak_kind = "cuBLAS bf16 sustained" if long_run else "cuBLAS bf16 burst"
+        achieved, unit, bound = flops_of(kind, M, N, K) / (ms * 1e-3) / 1e12, "TFLOP/s", "tensor"
+        peak = peaks["bf16_tflops_sustained"] if long_run else peaks["bf16_tflops"]
+        if kind in ("s8", "e4m3"):
+            peak, peak_kind = 2.0 * peak, peak_kind + " x2 (8-bit operands; no measured 8-bit peak)"
+        metric, munit = "GEMM TFLOP/s", "TFLOP/s"
+        e2e_val = total_flops / (e2e_ms * 1e-3) / 1e12
+
+    line = {
+        "metric": metric, "value": value, "unit": munit, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {"f16": "f16 (f32 accumulate)", "bf16": "bf16 (f32 accumulate)", "s8": "s8 (s32 accumulate)",
+                  "e4m3": "e4m3 (f32 accumulate)"}[kind],
+        "data": "synthetic", "config": workload_config(name, world), "clocks": clocks, "gpu_launches": args.steps,
+        "e2e": {"value": e2e_val, "unit": munit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_kind}, of {peak_src}",
+                     "kernel": "gemm_tcgen05_kernel" if not bytes_bound else "gemm_skinny_kernel",
+                     "kernel_ms": ms},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ho, _ = ge.load_oracle()
+        threads = os.cpu_count() or 1
+        val, rows, dt, tl = cpu_reference_rate(ho, np, M, N, K, seconds=12.0, threads=threads)
+        line["cpu_baseline"] = {
+            "value": val, "unit": "TFLOP/s", "cores": tl[0] * tl[1], "kind": "port",
+            "sample": f"first {rows} of {M} rows of C (N={N}, K={K}), fp32 inputs widened, threaded host gemm with "
+                      f"thread layout {tl}, {dt:.1f} s"}
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["also"] = extras(mb, torch, dev, peaks)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def extras(mb, torch, dev, peaks):
+    """The other configurations, each timed alone for a few launches (reported beside the headline)."""
+    out = {}
+    stream = torch.cuda.current_stream()
+    for name in ("gemm_f16_4096", "gemm_bf16_8192", "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192",
+                 "decode_bf16_16x28672x8192"):
+        kind, M, N, K, o = WORKLOADS[name]
+        nset = 3 if M <= 32 else 1  # rotate weight buffers for the HBM-bound decode shape
+        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i) for i in range(nset)]
+        kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
+        arrs = [(mb.MoYeArray(a), mb.MoYeArray(b), mb.MoYeArray(c)) for a, b, c in sets]
+        i = [0]
+
+        def fn():
+            a, b, c = arrs[i[0] % nset]
+            i[0] += 1
+            mb.matmul(a, b, c, **kw)
+
+        ms = time_launches(torch, fn, 20, 5, stream)
+        if M <= 32:
+            nbytes = (M * K + N * K + M * N) * 2
+            out[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+        else:
+            out[name] = {"ms": ms, "TFLOP/s": 2.0 * M * N * K / ms / 1e9}
+        del sets, arrs
+        torch.cuda.empty_cache()
+    out["copy_f16_8192"] = copy_rates(mb, torch, dev, peaks, 20, 5)
+    mb.synchronize_status(dev)
+    return out
+
+
+def copy_rates(mb, torch, dev, peaks, steps, warmup):
+    m = n = 8192
+    srcs = [(torch.rand(n, m, device=dev) * 2 - 1).half() for _ in range(4)]  # 4 x 134 MB > L2
+    dsts = [torch.zeros_like(s) for s in srcs]
+    lay = mb.make_layout((m, n))
+    res = {}
+    stream = torch.cuda.current_stream()
+    vec = mb.make_tiled_copy(mb.CopyAtom(mb.UniversalCopy(128), mb._lib.F16), mb.make_layout((16, 16)),
+                             mb.make_layout((8, 1)))
+    for label, tc in (("universal128", vec), ("tma", mb.make_tma_tiled_copy(mb._lib.F16, (128, 64)))):
+        pairs = [(mb.MoYeArray(d, lay), mb.MoYeArray(s, lay)) for d, s in zip(dsts, srcs)]
+        i = [0]
+
+        def fn():
+            d, s = pairs[i[0] % 4]
+            i[0] += 1
+            mb.copyto_(tc, d, s)
+
+        ms = time_launches(torch, fn, steps, warmup, stream)
+        gbs = 2.0 * m * n * 2 / ms / 1e6
+        res[label] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    return res
+
+
+def run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier):
+    sampler = ClockSampler(dev.index)
+    barrier()
+    sampler.start()
+    res = copy_rates(mb, torch, dev, peaks, args.steps, max(3, args.warmup))
+    barrier()
+    clocks = sampler.stop()
+    best = max(res.values(), key=lambda r: r["GB/s"])
+    t = torch.tensor([best["ms"]], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    nbytes = 2.0 * 8192 * 8192 * 2
+    line = {"metric": "copy GB/s", "value": nbytes * world / ms / 1e6, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 (bytes)", "data": "synthetic",
+            "config": {"workload": "copy_f16_8192", "tile": "128x64", "atoms": "128-bit", "sharding": f"row blocks x{world}",
+                       "l2": "4 rotating buffer pairs, 134 MB each"},
+            "clocks": clocks, "gpu_launches": args.steps * len(res), "kernels": res,
+            "roofline": {"bound": "hbm", "achieved": best["GB/s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": best["GB/s"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm copy, of {peak_src}"}}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm_f16_8192")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.steps < 1:
+        raise SystemExit("--steps must be >= 1")
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

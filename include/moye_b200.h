@@ -103,7 +103,7 @@ typedef enum {
 
 typedef struct {
   int32_t mode;                  /* moye_copy_mode_t */
-  int32_t tile_m;                /* tile extent along the contiguous mode; 0 = default (128) */
+  int32_t tile_m;                /* tile extent along the contiguous mode; 0 = default (256 bytes) */
   int32_t tile_n;                /* tile extent along the strided mode;    0 = default (64)  */
   int32_t flags;                 /* reserved, must be 0 */
 } moye_copy_params_t;

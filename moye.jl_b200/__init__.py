@@ -11,6 +11,7 @@ from .layout import *  # noqa: F401,F403
 from .array import *  # noqa: F401,F403
 from .atom import *  # noqa: F401,F403
 from .algorithm import *  # noqa: F401,F403
+from .sharding import *  # noqa: F401,F403
 from ._lib import MoyeError
 
 __version__ = "0.1.0"

@@ -51,10 +51,13 @@ def _as_rank2(x):
 
 
 def _tensor_arg(x, what):
+    if x._abi is not None:
+        return x._abi
     sd = _as_rank2(x)
     if sd is None:
         raise _lib.MoyeError(-3, f"{what} must be a rank-2 array with one stride per mode, got layout {x.layout}")
-    return _lib.make_tensor(x.ptr, x.dtype, sd[0], sd[1])
+    x._abi = _lib.make_tensor(x.ptr, x.dtype, sd[0], sd[1])
+    return x._abi
 
 
 def copyto_(*args, stream=None):
@@ -135,7 +138,7 @@ def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0
         if op.valtype_a != A.dtype or op.valtype_b != B.dtype:
             raise _lib.MoyeError(-2, f"{op} does not take these operand types")
         if tile_n == 0:
-            tile_n = tiled_mma.tile_size(1)
+            tile_n = op.shape_mnk[1]  # one atom per CTA: the tile is the instruction's N
     lib, h = _lib.load(), _lib.handle(dev.index)
     st = stream if stream is not None else current_stream_ptr(dev)
     p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, 0)
@@ -154,8 +157,16 @@ def matmul(A, B, C, **kw):
     if A.dtype not in _AB_TAG:
         raise _lib.MoyeError(-2, "matmul takes f16, bf16, s8 or e4m3 operands on sm_100a")
     n = C.layout.shape[1]
-    mma = make_tiled_mma(sm100_mma_op(_AB_TAG[A.dtype], 256 if n > 128 else (128 if n > 64 else 64)))
+    key = (A.dtype, 256 if n > 128 else (128 if n > 64 else 64))
+    mma = _MMA_CACHE.get(key)
+    if mma is None:
+        mma = _MMA_CACHE[key] = make_tiled_mma(sm100_mma_op(_AB_TAG[key[0]], key[1]))
+    if "tile_n" in kw and kw["tile_n"] == 0:
+        kw.pop("tile_n")
     return gemm_(mma, C, A, B, None, **kw)
+
+
+_MMA_CACHE = {}
 
 
 def layout_eval(layout, n=None, first=1, device=None, stream=None):

@@ -35,7 +35,7 @@ class MoYeArray:
     `MoYeArray(tensor)` with no layout takes the tensor's shape and strides.
     """
 
-    __slots__ = ("storage", "offset", "layout")
+    __slots__ = ("storage", "offset", "layout", "_abi")
 
     def __init__(self, data, layout=None, offset=0):
         if isinstance(data, MoYeArray):
@@ -56,6 +56,7 @@ class MoYeArray:
         if storage.dtype not in TORCH_TO_MOYE:
             raise TypeError(f"unsupported element type {storage.dtype}")
         self.storage, self.offset, self.layout = storage, int(offset), layout
+        self._abi = None  # cached C-ABI descriptor (the view is immutable)
 
     # -- engine
     @property

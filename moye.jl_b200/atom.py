@@ -26,7 +26,7 @@ from .layout import (COLON, Layout, _tup, append_layout, coalesce, composition, 
 __all__ = [
     "MMAOp", "CopyOp", "UniversalFMA", "UniversalCopy", "CPOP_ASYNC_CACHEALWAYS", "CPOP_TMA_LOAD_SW128",
     "CPOP_TMA_STORE", "MMAAtom", "TiledMMA", "ThrMMA", "make_tiled_mma", "CopyAtom", "TiledCopy", "ThrCopy",
-    "make_tiled_copy", "make_tiled_copy_A", "make_tiled_copy_B", "make_tiled_copy_C", "MMA_OPS", "mma_op",
+    "make_tiled_copy", "make_tma_tiled_copy", "make_tiled_copy_A", "make_tiled_copy_B", "make_tiled_copy_C", "MMA_OPS", "mma_op",
     "sm100_mma_op", "DTYPE_BITS",
 ]
 
@@ -374,6 +374,14 @@ def make_tiled_copy(copy_atom, thr_layout, val_layout=None):
     layout_mn = raked_product(thr_layout, val_layout, True)
     layout_tv = composition(right_inverse(layout_mn), make_layout((size(thr_layout), size(val_layout))))
     return TiledCopy(copy_atom, layout_tv, product_each(_tup(layout_mn.shape)))
+
+
+def make_tma_tiled_copy(dtype, tile=(128, 64), store=False):
+    """A TiledCopy whose single thread moves one whole `tile` with one TMA instruction:
+    thread layout 1, value layout = the tile."""
+    bits = DTYPE_BITS[dtype] * tile[0] * tile[1]
+    op = CPOP_TMA_STORE(bits) if store else CPOP_TMA_LOAD_SW128(bits)
+    return make_tiled_copy(CopyAtom(op, dtype), make_layout(1), make_layout(tuple(tile)))
 
 
 def make_tiled_copy_A(copy_atom, tiled_mma):

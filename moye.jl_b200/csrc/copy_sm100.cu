@@ -165,7 +165,8 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t*
   if (src->stride[0] != 1 || dst->stride[0] != 1)
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "tiled copy needs stride 1 along the first mode of both tensors");
   if (m > INT32_MAX / 4 || n > INT32_MAX / 4) MOYE_FAIL(MOYE_ERR_TOO_LARGE, "extent too large");
-  const int tile_m = p.tile_m ? p.tile_m : 128;
+  // default tile: 256-byte columns x 64 columns = 16 KB (128 x 64 for 2-byte elements)
+  const int tile_m = p.tile_m ? p.tile_m : (256 / eb > 0 ? 256 / eb : 1);
   const int tile_n = p.tile_n ? p.tile_n : 64;
   if (tile_m <= 0 || tile_n <= 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "bad tile");
   if (((uintptr_t)src->ptr & 15) || ((uintptr_t)dst->ptr & 15))

@@ -1,0 +1,119 @@
+# MoYeB200 -- host-level `gemm!` / `copyto!` methods for MoYe arrays in global memory, bound to
+# libmoye_b200 (include/moye_b200.h) with ccall.  Additive: nothing in MoYe changes.
+#
+# This file has never been executed: the image this library is built in has no Julia.  It is the
+# binding a MoYe maintainer would add; the same calls are exercised from Python (ctypes) by the tests.
+module MoYeB200
+
+using MoYe, CUDA, Libdl
+using MoYe: MoYeArray, ViewEngine, Layout, TiledMMA, TiledCopy, AbstractMMAOP, AbstractCopyOp,
+            flatten, coalesce, shape, stride, layout, rank
+
+const libmoye_b200 = Ref{String}(get(ENV, "MOYE_B200_LIB", "libmoye_b200.so"))
+
+# ---- C structs (include/moye_b200.h)
+struct MoyeTensor
+    ptr::Ptr{Cvoid}
+    dtype::Int32
+    rank::Int32
+    shape::NTuple{4, Int64}
+    stride::NTuple{4, Int64}
+end
+struct MoyeGemmParams
+    alpha::Float32; beta::Float32; scale_a::Float32; scale_b::Float32
+    tile_n::Int32; split_k::Int32; path::Int32; flags::Int32
+end
+struct MoyeCopyParams
+    mode::Int32; tile_m::Int32; tile_n::Int32; flags::Int32
+end
+
+primitive type E4M3 8 end   # MoYe has no fp8 type; bits only
+
+moye_dtype(::Type{Float32}) = Int32(0); moye_dtype(::Type{Float16}) = Int32(1)
+moye_dtype(::Type{MoYe.BFloat16}) = Int32(2); moye_dtype(::Type{Int8}) = Int32(3)
+moye_dtype(::Type{UInt8}) = Int32(4); moye_dtype(::Type{E4M3}) = Int32(5); moye_dtype(::Type{Int32}) = Int32(6)
+
+# ---- the gap MoYe leaves on the host side: arrays over device pointers (src/engine.jl:10-15 only
+# wraps Ptr and LLVMPtr; src/pointer.jl:1 only recognises LLVMPtr{..., AS.Global} as global memory)
+MoYe.ViewEngine(p::CuPtr{T}) where {T} = ViewEngine{T, CuPtr{T}}(p, 0)          # hypothetical ctor
+MoYe.MoYeArray(A::CuArray{T}, l::Layout) where {T} = MoYeArray(ViewEngine(pointer(A)), l)
+MoYe.MoYeArray(A::CuArray{T}, s::Tuple) where {T} = MoYeArray(A, MoYe.make_layout(s))
+MoYe.isgmem(::MoYeArray{T, N, ViewEngine{T, CuPtr{T}}}) where {T, N} = true
+
+# ---- new ops (MoYe's naming: src/arch/mma/make_mma_ops.jl:368, src/arch/copy/copy_async.jl:8)
+abstract type AbstractSM100MMAOP{D, A, B, C} <: AbstractMMAOP{D, A, B, C} end
+struct MMAOP_SM100_128x256x16_F32F16F16F32_SS <: AbstractSM100MMAOP{Float32, Float16, Float16, Float32} end
+struct MMAOP_SM100_128x256x16_F32BF16BF16F32_SS <: AbstractSM100MMAOP{Float32, MoYe.BFloat16, MoYe.BFloat16, Float32} end
+struct MMAOP_SM100_128x256x32_S32S8S8S32_SS <: AbstractSM100MMAOP{Int32, Int8, Int8, Int32} end
+struct MMAOP_SM100_128x256x32_F32E4M3E4M3F32_SS <: AbstractSM100MMAOP{Float32, E4M3, E4M3, Float32} end
+struct CPOP_TMA_LOAD_SW128 <: AbstractCopyOp{Registers{UInt128, 1}, Registers{UInt128, 1}} end
+struct CPOP_TMA_STORE <: AbstractCopyOp{Registers{UInt128, 1}, Registers{UInt128, 1}} end
+# one thread issues a tcgen05 instruction for the whole CTA tile; the accumulator lives in tensor memory
+MoYe.thr_id(::MoYe.MMATraits{<:AbstractSM100MMAOP}) = MoYe.@Layout 1
+MoYe.shape_mnk(::MMAOP_SM100_128x256x16_F32F16F16F32_SS) = MoYe.static((128, 256, 16))
+MoYe.shape_mnk(::MMAOP_SM100_128x256x16_F32BF16BF16F32_SS) = MoYe.static((128, 256, 16))
+MoYe.shape_mnk(::MMAOP_SM100_128x256x32_S32S8S8S32_SS) = MoYe.static((128, 256, 32))
+MoYe.shape_mnk(::MMAOP_SM100_128x256x32_F32E4M3E4M3F32_SS) = MoYe.static((128, 256, 32))
+
+# ---- descriptor flattening: layout(x) -> (shape, stride) of a rank-2 view, 0-based element strides
+function moye_tensor(x::MoYeArray{T}) where {T}
+    l = layout(x)
+    rank(l) == 2 || error("libmoye_b200 takes rank-2 arrays")
+    m1, m2 = coalesce(l[1]), coalesce(l[2])
+    (rank(m1) == 1 && rank(m2) == 1) || error("each mode must be describable by one stride")
+    MoyeTensor(Ptr{Cvoid}(UInt(pointer(x))), moye_dtype(T), Int32(2),
+               (Int64(shape(m1)), Int64(shape(m2)), 0, 0), (Int64(stride(m1)), Int64(stride(m2)), 0, 0))
+end
+
+const handles = Dict{Tuple{Int, Int}, Ptr{Cvoid}}()
+function handle()
+    key = (Threads.threadid(), CUDA.deviceid(CUDA.device()))
+    get!(handles, key) do
+        h = Ref{Ptr{Cvoid}}(C_NULL)
+        check(ccall((:moye_b200_create, libmoye_b200[]), Cint, (Ref{Ptr{Cvoid}},), h))
+        h[]
+    end
+end
+check(rc) = rc == 0 ? nothing :
+    error("libmoye_b200 ($rc): " * unsafe_string(ccall((:moye_b200_last_error, libmoye_b200[]), Cstring, ())))
+
+# ---- gemm!(tiled_mma, D, A, B, C): replaces the whole matmul_kernel of examples/gemm.jl:4-64
+function MoYe.gemm!(mma::TiledMMA{<:MoYe.MMAAtom{<:MoYe.MMATraits{<:AbstractSM100MMAOP}}},
+                    D::MoYeArray, A::MoYeArray, B::MoYeArray, C::Union{MoYeArray, Nothing} = nothing;
+                    alpha = 1, beta = 0, scale_a = 1f0, scale_b = 1f0, stream = CUDA.stream())
+    all(MoYe.isgmem, (D, A, B)) || error("host-level gemm! needs global-memory arrays (no CPU fallback)")
+    p = Ref(MoyeGemmParams(alpha, beta, scale_a, scale_b, Int32(MoYe.tile_size(mma, MoYe._2)), 0, 0, 0))
+    tD, tA, tB = Ref(moye_tensor(D)), Ref(moye_tensor(A)), Ref(moye_tensor(B))
+    tC = (C === nothing || iszero(beta)) ? C_NULL : Ref(moye_tensor(C))
+    check(ccall((:moye_b200_gemm, libmoye_b200[]), Cint,
+                (Ptr{Cvoid}, Ref{MoyeTensor}, Ref{MoyeTensor}, Ref{MoyeTensor}, Ptr{Cvoid}, Ref{MoyeGemmParams}, Ptr{Cvoid}),
+                handle(), tD, tA, tB, tC, p, stream.handle))
+    return D
+end
+
+# ---- copyto!(tiled_copy, dst, src): replaces copy_kernel of test/host/copy_async.jl:3-25
+function Base.copyto!(tc::TiledCopy, dst::MoYeArray{T, 2, ViewEngine{T, CuPtr{T}}},
+                      src::MoYeArray{T, 2, ViewEngine{T, CuPtr{T}}}; stream = CUDA.stream()) where {T}
+    tiler = MoYe.tile_size(tc)
+    mode = MoYe.get_traits(tc).copy_op isa CPOP_TMA_LOAD_SW128 ? Int32(2) : Int32(1)
+    p = Ref(MoyeCopyParams(mode, Int32(tiler[1]), Int32(max(tiler[2], 64)), 0))
+    check(ccall((:moye_b200_copy, libmoye_b200[]), Cint,
+                (Ptr{Cvoid}, Ref{MoyeTensor}, Ref{MoyeTensor}, Ref{MoyeCopyParams}, Ptr{Cvoid}),
+                handle(), Ref(moye_tensor(dst)), Ref(moye_tensor(src)), p, stream.handle))
+    return dst
+end
+
+# ---- matmul(A, B, C) of examples/gemm.jl:66-89, on the tcgen05 atom for eltype(A)
+function matmul(A::CuMatrix{Float16}, B::CuMatrix{Float16}, C::CuMatrix{Float32})
+    # K-major views of row-major storage: pass transposed CuArrays, e.g. A = CuArray(A_host')'
+    mma = MoYe.make_tiled_mma(MMAOP_SM100_128x256x16_F32F16F16F32_SS())
+    MoYe.gemm!(mma, MoYeArray(C, size(C)), MoYeArray(A, size(A)), MoYeArray(B, size(B)))
+end
+
+"Synchronise and surface a device-side bounded-wait failure (moye_b200_status)."
+function status(stream = CUDA.stream())
+    site = Ref{Int32}(0)
+    check(ccall((:moye_b200_status, libmoye_b200[]), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Ref{Int32}), handle(), stream.handle, site))
+end
+
+end # module

@@ -1,0 +1,73 @@
+"""The C ABI as a binary contract: the library loads without a GPU, exports every symbol the
+header declares, refuses to create a handle when no device exists (there is no CPU path),
+and its structs have the layout the ctypes binding assumes."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "moye_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moye_b200_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_declares_expected_entry_points():
+    names = declared_functions()
+    for n in ("moye_b200_create", "moye_b200_destroy", "moye_b200_gemm", "moye_b200_copy", "moye_b200_layout_copy",
+              "moye_b200_layout_eval", "moye_b200_status", "moye_b200_last_error", "moye_b200_version"):
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol(mb):
+    lib = mb._lib.load()
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in include/moye_b200.h but not exported"
+        assert name in mb._lib.EXPORTS, f"{name} has no ctypes prototype"
+    assert lib.moye_b200_version() == 100
+
+
+def test_header_compiles_as_c(tmp_path):
+    src = tmp_path / "t.c"
+    src.write_text('#include "moye_b200.h"\nint main(void){moye_tensor_t t; moye_gemm_params_t p; (void)t; (void)p; '
+                   "return sizeof(moye_layout_t) == 8 + 2 * 8 * MOYE_MAX_FLAT_RANK ? 0 : 1;}\n")
+    exe = tmp_path / "t"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)],
+                   check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_struct_layouts(mb):
+    L = mb._lib
+    assert ctypes.sizeof(L.Tensor) == 8 + 4 + 4 + 8 * 4 + 8 * 4
+    assert ctypes.sizeof(L.FlatLayout) == 8 + 16 * L.MAX_FLAT_RANK
+    assert ctypes.sizeof(L.GemmParams) == 32 and ctypes.sizeof(L.CopyParams) == 16
+    assert L.Tensor.shape.offset == 16 and L.Tensor.stride.offset == 48
+
+
+def test_no_device_is_an_error_not_a_fallback(mb):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    lib = mb._lib.load()
+    out = ctypes.c_void_p()
+    rc = lib.moye_b200_create(ctypes.byref(out))
+    assert rc == -8 and not out.value
+    assert b"no CPU path" in lib.moye_b200_last_error()
+    assert lib.moye_b200_destroy(None) == 0
+
+
+def test_product_does_not_import_the_oracle():
+    """The package must not reach into oracle/ (the oracle is the checker, never the product)."""
+    pkg = os.path.join(ROOT, "moye.jl_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower().replace("no cpu", ""), f"{f} mentions the oracle"
