@@ -156,6 +156,33 @@ int moye_b200_layout_copy(moye_handle_t h, void* dst, const moye_layout_t* dst_l
 int moye_b200_layout_eval(moye_handle_t h, const moye_layout_t* layout, int64_t first,
                           int64_t n, int64_t* out, void* stream);
 
+/* D(M,N) = alpha * A(M,K) . B(N,K)^T for M <= 32 (the decode shape), for callers that must
+ * not allocate.  It has no counterpart in the reference.
+ *
+ * The other GEMM entry point keeps its stream-K scratch in memory the handle obtains with
+ * cudaMalloc (and creating a handle allocates too).  Some callers cannot do that: a serving
+ * loop whose device memory was fully handed out at start-up, a plugin bound by a "no
+ * allocation after initialisation" rule, or code that simply has no handle.  This entry point
+ * takes no handle and calls no cudaMalloc / cudaFree or any other allocating routine: its
+ * scratch (tickets, fp32 partial tiles, a status word; 5.02 MiB) is a static device array
+ * inside the library, which every GPU that loads the library holds until the process exits.
+ *
+ * Limits (errors, with a message, beyond them): M <= 32, N <= 524288 (4096 row blocks of W),
+ * at most 160 SMs.  A, B f16 or bf16, K-major, 16-byte-aligned rows; D f32 or the operand type,
+ * any strides.  beta is 0 (C is not read).
+ *
+ * The first call on a device (with that device current) looks up the array's device address
+ * and raises the kernels' shared-memory limit; make that first call before any stream capture.
+ * All calls share the one array and it keeps the previous call's contents: each call clears
+ * the part that must start at zero on `stream` before its kernel.  Two calls that overlap on
+ * the GPU (different streams, or different host threads without ordering) race on it; order
+ * them on one stream or with events.
+ *
+ * device_status: optional device int32 that receives a wait-site code if a bounded wait in
+ * the kernel gives up (0 otherwise; the caller clears it); NULL keeps that word inside the array. */
+int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                                 float alpha, int32_t* device_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

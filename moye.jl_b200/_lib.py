@@ -68,6 +68,9 @@ EXPORTS = {
     "moye_b200_layout_copy": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(FlatLayout),
                                              ctypes.c_void_p, ctypes.POINTER(FlatLayout), ctypes.c_int32,
                                              ctypes.c_void_p]),
+    "moye_b200_gemm_skinny_static": (ctypes.c_int, [ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
+                                                    ctypes.POINTER(Tensor), ctypes.c_float, ctypes.c_void_p,
+                                                    ctypes.c_void_p]),
     "moye_b200_layout_eval": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(FlatLayout), ctypes.c_int64,
                                              ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
 }

@@ -20,7 +20,8 @@ from .array import MoYeArray, isgmem
 from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
 from .layout import Layout, coalesce, size
 
-__all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr"]
+__all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
+           "gemm_skinny_static_"]
 
 
 def current_stream_ptr(device=None):
@@ -189,3 +190,27 @@ def synchronize_status(device=None, stream=None):
     st = stream if stream is not None else current_stream_ptr(device)
     site = ctypes.c_int32(0)
     _lib.check(lib.moye_b200_status(h, st, ctypes.byref(site)))
+
+
+def gemm_skinny_static_(D, A, B, alpha=1.0, device_status=None, stream=None):
+    """D = alpha * A . B^T for a decode-shaped product (A has at most 32 rows) through the
+    entry point that allocates nothing (`moye_b200_gemm_skinny_static`).
+
+    Meant for callers that may not allocate device memory once they are running -- a serving
+    loop with a fixed memory budget, a plugin under a no-allocation rule, code without a
+    library handle: the stream-K scratch is a 5 MiB static array inside the library instead of
+    handle-owned memory.  Limits: A.rows <= 32, B.rows <= 524288.  All calls share that one
+    array, so calls that could overlap on the GPU must be ordered (same stream or events); the
+    first call on a device does a one-time set-up and should happen before any stream capture.
+    `device_status` may be a 1-element int32 CUDA tensor that receives a non-zero code if a
+    bounded wait inside the kernel gave up.
+    """
+    D, A, B = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (D, A, B))
+    dev = _need_gmem(D, A, B)
+    st = stream if stream is not None else current_stream_ptr(dev)
+    status_ptr = ctypes.c_void_p(device_status.data_ptr()) if device_status is not None else None
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().moye_b200_gemm_skinny_static(
+            ctypes.byref(_tensor_arg(D, "D")), ctypes.byref(_tensor_arg(A, "A")), ctypes.byref(_tensor_arg(B, "B")),
+            ctypes.c_float(alpha), status_ptr, st))
+    return D

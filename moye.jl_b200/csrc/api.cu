@@ -96,6 +96,30 @@ int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype,
   return MOYE_OK;
 }
 
+// Encodes a rank-2 tiled tensor map straight into `out`: no handle, no cache, no heap.
+int encode_tmap_2d_uncached(CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
+                            uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) MOYE_FAIL(MOYE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMapDataType tdt;
+  if (!tmap_dtype(dtype, &tdt)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "dtype %d has no tensor-map type", dtype);
+  const int eb = dtype_bytes(dtype);
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0)
+    MOYE_FAIL(MOYE_ERR_MISALIGNED, "tensor base %p is not 16-byte aligned", ptr);
+  if (dim1 > 1 && (stride1_bytes & 15) != 0)
+    MOYE_FAIL(MOYE_ERR_MISALIGNED, "row pitch of %llu bytes is not a multiple of 16",
+              (unsigned long long)stride1_bytes);
+  cuuint64_t dims[2] = {dim0, dim1};
+  cuuint64_t strides[1] = {dim1 > 1 ? stride1_bytes : (cuuint64_t)((dim0 * eb + 15) / 16 * 16)};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, tdt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) MOYE_FAIL(MOYE_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return MOYE_OK;
+}
+
 int ensure_workspace(moye_b200_ctx* h, size_t bytes) {
   if (bytes <= h->workspace_bytes) return MOYE_OK;
   if (h->workspace) {

@@ -87,6 +87,9 @@ namespace moye {
 int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
                  uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);
 
+int encode_tmap_2d_uncached(CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
+                            uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);
+
 // Grows the handle-owned workspace to at least `bytes` (never shrinks).
 int ensure_workspace(moye_b200_ctx* h, size_t bytes);
 

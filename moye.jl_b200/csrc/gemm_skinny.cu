@@ -329,4 +329,147 @@ int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tens
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// The same stream-K kernel for callers that are not allowed to allocate device memory.
+//
+// Who that is: code running where cudaMalloc is off limits -- a host thread inside a
+// latency-critical serving loop whose memory was carved up at start-up, a plugin that a host
+// application loads under a "no allocations after initialisation" rule, or a caller that
+// never created a handle (moye_b200_create allocates the status word and, later, the
+// workspace).  For them the stream-K scratch (tickets + fp32 partial tiles + a status word)
+// lives in this file-scope device array instead of the handle's workspace.  Every GPU that
+// loads the library carries these bytes until the process exits.
+constexpr int kStaticMaxSms = 160;          // CTAs the partial area is sized for (B200 has 148)
+constexpr int kStaticMaxNx = 32;            // padded rows of X
+constexpr int kStaticMaxRowBlocks = 4096;   // row blocks of W, i.e. N <= 524288
+constexpr size_t kStaticStatusBytes = 256;
+constexpr size_t kStaticTicketBytes = kStaticMaxRowBlocks * sizeof(int);
+constexpr size_t kStaticPartialBytes = (size_t)kStaticMaxSms * 2 * kStaticMaxNx * 128 * sizeof(float);
+constexpr size_t kStaticScratchBytes = kStaticStatusBytes + kStaticTicketBytes + kStaticPartialBytes;  // 5.02 MiB
+
+static __device__ __align__(256) unsigned char g_skinny_scratch[kStaticScratchBytes];
+
+// In host code `g_skinny_scratch` is only a stand-in for the symbol, not an address the GPU
+// understands; the device address is looked up once per device and kept here.
+struct StaticSetup {
+  bool ready = false;
+  unsigned char* base = nullptr;
+  int num_sms = 0;
+};
+static StaticSetup g_static_setup[64];
+static std::mutex g_static_mu;
+
+template <typename OutT, int NX>
+static int configure_skinny_kernel() {
+  constexpr int STAGE = 128 * 128 + NX * 128;
+  constexpr int STAGES = (227 * 1024 - 1024 - 512) / STAGE;
+  constexpr int SMEM = STAGES * STAGE + 512 + 1024;
+  MOYE_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel<OutT, NX, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM));
+  return MOYE_OK;
+}
+
+// First use on a device (that device being current): resolve the scratch address, size the grid,
+// raise the kernels' shared-memory limit.  Nothing here allocates.
+static int static_setup_for_current_device(StaticSetup** out) {
+  int dev = -1;
+  MOYE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  StaticSetup& s = g_static_setup[dev];
+  if (!s.ready) {
+    int major = 0, sms = 0;
+    MOYE_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) MOYE_FAIL(MOYE_ERR_NO_DEVICE, "device %d is not sm_100", dev);
+    MOYE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    void* p = nullptr;
+    MOYE_CUDA(cudaGetSymbolAddress(&p, g_skinny_scratch));
+    if (int rc = configure_skinny_kernel<float, 16>()) return rc;
+    if (int rc = configure_skinny_kernel<__half, 16>()) return rc;
+    if (int rc = configure_skinny_kernel<__nv_bfloat16, 16>()) return rc;
+    if (int rc = configure_skinny_kernel<float, 32>()) return rc;
+    if (int rc = configure_skinny_kernel<__half, 32>()) return rc;
+    if (int rc = configure_skinny_kernel<__nv_bfloat16, 32>()) return rc;
+    s.base = static_cast<unsigned char*>(p);
+    s.num_sms = sms;
+    s.ready = true;
+  }
+  *out = &s;
+  return MOYE_OK;
+}
+
+template <typename OutT, int NX>
+static void launch_skinny_static(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyArgs& a, int grid,
+                                 cudaStream_t stream) {
+  constexpr int STAGE = 128 * 128 + NX * 128;
+  constexpr int STAGES = (227 * 1024 - 1024 - 512) / STAGE;
+  constexpr int SMEM = STAGES * STAGE + 512 + 1024;
+  gemm_skinny_kernel<OutT, NX, STAGES><<<grid, 192, SMEM, stream>>>(tw, tx, a);
+}
+
 }  // namespace moye
+
+extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
+                                            float alpha, int32_t* device_status, void* stream_) {
+  using namespace moye;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!D || !A || !B) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "D, A and B must be non-null");
+  if (A->rank != 2 || B->rank != 2 || D->rank != 2) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "A, B, D must be rank 2");
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (B->shape[1] != K || D->shape[0] != M || D->shape[1] != N) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "shape mismatch");
+  if (M <= 0 || N <= 0 || K <= 0) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "empty GEMM");
+  if (!A->ptr || !B->ptr || !D->ptr) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "null data pointer");
+  if (A->dtype != B->dtype || (A->dtype != MOYE_F16 && A->dtype != MOYE_BF16))
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "operands must both be f16 or both bf16");
+  const int out = D->dtype;
+  if (!(out == MOYE_F32 || (out == MOYE_F16 && A->dtype == MOYE_F16) || (out == MOYE_BF16 && A->dtype == MOYE_BF16)))
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
+  if (A->stride[1] != 1 || B->stride[1] != 1)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B must be K-major (stride 1 along K)");
+  if (M > kStaticMaxNx)
+    MOYE_FAIL(MOYE_ERR_TOO_LARGE, "M = %lld exceeds the %d rows the static scratch is sized for", (long long)M,
+              kStaticMaxNx);
+  if (K > INT32_MAX / 2 || N > (int64_t)kStaticMaxRowBlocks * 128)
+    MOYE_FAIL(MOYE_ERR_TOO_LARGE, "N = %lld exceeds the %lld rows of W the static scratch is sized for (%d row blocks)",
+              (long long)N, (long long)kStaticMaxRowBlocks * 128, kStaticMaxRowBlocks);
+  StaticSetup* su = nullptr;
+  if (int rc = static_setup_for_current_device(&su)) return rc;
+  if (su->num_sms > kStaticMaxSms)
+    MOYE_FAIL(MOYE_ERR_TOO_LARGE, "%d SMs exceed the %d the static scratch is sized for", su->num_sms, kStaticMaxSms);
+
+  const int nx = M <= 16 ? 16 : 32;
+  CUtensorMap tw, tx;
+  if (int rc = encode_tmap_2d_uncached(&tw, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * 2, 64, 128, true)) return rc;
+  if (int rc = encode_tmap_2d_uncached(&tx, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * 2, 64, nx, true)) return rc;
+
+  SkinnyArgs a;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K;
+  a.n_tiles = (int)((N + 127) / 128);
+  a.k_blocks = (int)((K + 63) / 64);
+  a.units = (long long)a.n_tiles * a.k_blocks;
+  const uint32_t fmt = A->dtype == MOYE_BF16 ? 1u : 0u;
+  a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(nx >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  a.alpha = alpha;
+  a.D = D->ptr;
+  a.d_sm = D->stride[0];
+  a.d_sn = D->stride[1];
+  a.status = device_status ? device_status : reinterpret_cast<int*>(su->base);
+  a.tickets = reinterpret_cast<int*>(su->base + kStaticStatusBytes);
+  a.partials = reinterpret_cast<float*>(su->base + kStaticStatusBytes + kStaticTicketBytes);
+  // The array keeps whatever the previous call left: the tickets (and the built-in status word)
+  // must read zero when the kernel starts, the partial tiles are always written before they are read.
+  MOYE_CUDA(cudaMemsetAsync(su->base, 0, kStaticStatusBytes + (size_t)a.n_tiles * sizeof(int), stream));
+  long long grid = su->num_sms;
+  if (grid > a.units) grid = a.units;
+  if (nx == 16) {
+    if (out == MOYE_F32) launch_skinny_static<float, 16>(tw, tx, a, (int)grid, stream);
+    else if (out == MOYE_F16) launch_skinny_static<__half, 16>(tw, tx, a, (int)grid, stream);
+    else launch_skinny_static<__nv_bfloat16, 16>(tw, tx, a, (int)grid, stream);
+  } else {
+    if (out == MOYE_F32) launch_skinny_static<float, 32>(tw, tx, a, (int)grid, stream);
+    else if (out == MOYE_F16) launch_skinny_static<__half, 32>(tw, tx, a, (int)grid, stream);
+    else launch_skinny_static<__nv_bfloat16, 32>(tw, tx, a, (int)grid, stream);
+  }
+  MOYE_CUDA(cudaGetLastError());
+  return MOYE_OK;
+}
