@@ -21,7 +21,7 @@ from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
 from .layout import Layout, coalesce, size
 
 __all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
-           "gemm_skinny_static_"]
+           "gemm_skinny_static_", "plan_gemm", "plan_copy", "LaunchPlan"]
 
 
 def current_stream_ptr(device=None):
@@ -168,6 +168,80 @@ def matmul(A, B, C, **kw):
 
 
 _MMA_CACHE = {}
+
+
+class LaunchPlan:
+    """A prepared call: every argument of the C entry point is built once, so repeating the
+    launch costs one foreign call.  Kernel authors in MoYe pay the tiling cost at compile time
+    (static layouts); this is the host-level analogue for a caller that launches the same
+    operation many times (a benchmark loop, a serving step).  The arrays are kept alive by the
+    plan.  `plan()` launches on the current stream, `plan(stream_ptr)` on the given one."""
+
+    __slots__ = ("_fn", "_args", "_device", "_keep")
+
+    def __init__(self, fn, args, device, keep):
+        self._fn, self._args, self._device, self._keep = fn, args, device, keep
+
+    def __call__(self, stream=None):
+        rc = self._fn(*self._args, stream if stream is not None else current_stream_ptr(self._device))
+        if rc:
+            _lib.check(rc)
+
+
+def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0):
+    """`gemm_` with the argument marshalling done once; returns a `LaunchPlan`."""
+    tiled_mma = None
+    if args and isinstance(args[0], TiledMMA):
+        tiled_mma, args = args[0], args[1:]
+    if len(args) == 3:
+        A, B, C = args
+        D = C
+    else:
+        D, A, B, C = args
+    D, A, B = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (D, A, B))
+    if C is not None and not isinstance(C, MoYeArray):
+        C = MoYeArray(C)
+    use_c = C is not None and beta != 0.0
+    dev = _need_gmem(*([D, A, B] + ([C] if use_c else [])))
+    if tiled_mma is not None:
+        op = tiled_mma.atom.op
+        if op.arch != "sm_100a" or op.valtype_a != A.dtype or op.valtype_b != B.dtype:
+            raise _lib.MoyeError(-2, f"{op} cannot multiply these operands on sm_100a")
+        tile_n = tile_n or op.shape_mnk[1]
+    lib, h = _lib.load(), _lib.handle(dev.index)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, 0)
+    tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
+    tC = _tensor_arg(C, "C") if use_c else None
+    argv = (h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB), ctypes.byref(tC) if use_c else None,
+            ctypes.byref(p))
+    return LaunchPlan(lib.moye_b200_gemm, argv, dev, (D, A, B, C, p, tD, tA, tB, tC))
+
+
+def plan_copy(*args):
+    """`copyto_([tiled_copy,] dst, src)` for the tiled (rank-2, contiguous first mode) case, prepared once."""
+    if len(args) == 3:
+        tiled_copy, dst, src = args
+    else:
+        (dst, src), tiled_copy = args, None
+    dev = _need_gmem(dst, src)
+    sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
+    if sd_d is None or sd_s is None or sd_d[0] != sd_s[0] or sd_d[1][0] != 1 or sd_s[1][0] != 1:
+        raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode")
+    if dst.storage.dtype != src.storage.dtype:
+        raise _lib.MoyeError(-2, "copyto!: element types differ")
+    params = None
+    if tiled_copy is not None:
+        mode = tiled_copy.copy_atom.op.mode
+        if mode is None:
+            raise _lib.MoyeError(-3, f"{tiled_copy.copy_atom.op} is narrower than 128 bits")
+        tm = tiled_copy.tiler_mn[0]
+        tn = tiled_copy.tiler_mn[1] if len(tiled_copy.tiler_mn) > 1 else 1
+        params = _lib.CopyParams(mode, tm, max(tn, 64) if mode == _lib.COPY_UNIVERSAL128 else tn, 0)
+    lib, h = _lib.load(), _lib.handle(dev.index)
+    td = _lib.make_tensor(dst.ptr, dst.dtype, sd_d[0], sd_d[1])
+    ts = _lib.make_tensor(src.ptr, src.dtype, sd_s[0], sd_s[1])
+    argv = (h, ctypes.byref(td), ctypes.byref(ts), ctypes.byref(params) if params is not None else None)
+    return LaunchPlan(lib.moye_b200_copy, argv, dev, (dst, src, td, ts, params))
 
 
 def layout_eval(layout, n=None, first=1, device=None, stream=None):

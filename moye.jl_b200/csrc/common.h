@@ -9,6 +9,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 
 #include "../../include/moye_b200.h"
 
@@ -75,6 +76,7 @@ struct moye_b200_ctx {
   size_t workspace_bytes = 0;
   std::mutex mu;
   std::unordered_map<moye::TmapKey, CUtensorMap, moye::TmapKeyHash> tmaps;
+  std::unordered_set<const void*> configured;   // kernels whose dynamic-smem limit is already raised
 };
 
 namespace moye {
@@ -89,6 +91,20 @@ int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype,
 
 int encode_tmap_2d_uncached(CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
                             uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);
+
+// Raises a kernel's dynamic shared-memory limit the first time this handle launches it.
+template <typename K>
+inline int configure_once(moye_b200_ctx* h, K kernel, int smem_bytes) {
+  const void* key = reinterpret_cast<const void*>(kernel);
+  {
+    std::lock_guard<std::mutex> lk(h->mu);
+    if (h->configured.count(key)) return MOYE_OK;
+  }
+  MOYE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  std::lock_guard<std::mutex> lk(h->mu);
+  h->configured.insert(key);
+  return MOYE_OK;
+}
 
 // Grows the handle-owned workspace to at least `bytes` (never shrinks).
 int ensure_workspace(moye_b200_ctx* h, size_t bytes);

@@ -228,7 +228,7 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t*
     a.status = h->d_status;
     const size_t smem = (size_t)tile_bytes * SLOTS + 128 + SLOTS * 8;
     auto kern = copy_tma_kernel<SLOTS, LOOK>;
-    MOYE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (int rc = configure_once(h, kern, (int)smem)) return rc;
     long long grid = a.tiles < (long long)h->num_sms * 2 ? a.tiles : (long long)h->num_sms * 2;
     kern<<<(int)grid, 32, smem, stream>>>(ts, td, a);
     MOYE_CUDA(cudaGetLastError());

@@ -269,7 +269,7 @@ static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUt
   constexpr int STAGES = (227 * 1024 - 1024 - 512) / STAGE;
   constexpr int SMEM = STAGES * STAGE + 512 + 1024;
   auto kern = gemm_skinny_kernel<OutT, NX, STAGES>;
-  MOYE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
   long long grid = h->num_sms;
   if (grid > a.units) grid = a.units;
   // workspace: a fixed ticket area (zero at rest: the kernel restores it) then the partial slots

@@ -60,6 +60,109 @@ __device__ __forceinline__ float load_c_as_float(const void* C, long long off) {
   return static_cast<float>(reinterpret_cast<const OutT*>(C)[off]);
 }
 
+
+// Epilogue of one accumulator tile for one warp: its 32 TMEM lanes x BN columns go
+// TMEM -> registers -> (alpha, beta, convert) -> staging tile in shared memory -> TMA store.
+// After the last TMEM read the accumulator is handed back: an arrive on `acc_empty_local`, or,
+// when `acc_empty_remote` is non-zero, on that shared::cluster address (the pair leader's barrier).
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorMap* tmD, uint32_t t_addr, int m0,
+                                              int n0, uint8_t* my_buf, int& nstore, int lane,
+                                              uint64_t* acc_empty_local, uint32_t acc_empty_remote) {
+  constexpr int EPI_BUF = 4096;
+  constexpr bool INT_OUT = (KIND == KIND_I8);
+  // columns handled per TMA store: a 128-byte row for N-major output, 32 for M-major
+  constexpr int SC = OUT_M_MAJOR ? 32 : (128 / (int)sizeof(OutT));
+  constexpr int SUB = SC / 32;
+#pragma unroll 1
+  for (int c = 0; c < BN / SC; ++c) {
+    uint8_t* sb = my_buf + (nstore & 1) * EPI_BUF;
+    if (lane == 0) tma_store_wait_read<1>();  // the store that last used `sb` has drained
+    __syncwarp();
+#pragma unroll
+    for (int s = 0; s < SUB; ++s) {
+      uint32_t v[32];
+      const int col0 = c * SC + s * 32;
+      tmem_ld_x32(t_addr + col0, v);
+      tmem_ld_wait();
+      if (c == BN / SC - 1 && s == SUB - 1) {
+        // last read of this accumulator: hand it back to the MMA warp
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (acc_empty_remote != 0u) mbar_arrive_remote(acc_empty_remote);
+          else mbar_arrive(acc_empty_local);
+        }
+      }
+      if (g.beta != 0.f) {
+        const int row = m0 + lane;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = n0 + col0 + j;
+          if (row < g.M && col < g.N) {
+            const long long off = (long long)row * g.c_sm + (long long)col * g.c_sn;
+            if constexpr (INT_OUT) {
+              v[j] = (uint32_t)((int)v[j] + reinterpret_cast<const int*>(g.C)[off]);
+            } else {
+              float cin = load_c_as_float<OutT>(g.C, off);
+              v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha + g.beta * cin);
+            }
+          }
+        }
+      } else if constexpr (!INT_OUT) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha);
+      }
+      if constexpr (OUT_M_MAJOR) {
+        // staging tile is [32 columns][32 rows], rows contiguous: conflict-free
+        if constexpr (INT_OUT) {
+          int* so = reinterpret_cast<int*>(sb);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) so[j * 32 + lane] = (int)v[j];
+        } else {
+          OutT* so = reinterpret_cast<OutT*>(sb);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) so[j * 32 + lane] = cvt_out<OutT>(__uint_as_float(v[j]));
+        }
+      } else {
+        // staging tile is [32 rows][128 bytes] in the 128-byte swizzle the store map expects
+        uint8_t* rowp = sb + lane * 128;
+        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              OutT lo = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e]));
+              OutT hi = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e + 1]));
+              w[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) |
+                     ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+            }
+            const int chunk = s * 4 + j;
+            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if constexpr (OUT_M_MAJOR)
+        tma_store_2d(tmD, sb, m0, n0 + c * SC);
+      else
+        tma_store_2d(tmD, sb, n0 + c * SC, m0);
+      tma_store_commit();
+    }
+    ++nstore;
+  }
+}
+
 template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -73,7 +176,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int EPI_BUF = 4096;        // one staging buffer of one epilogue warp
   constexpr uint32_t TMEM_COLS = 2 * BN;
-  constexpr bool INT_OUT = (KIND == KIND_I8);
   static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile N");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
 
@@ -180,94 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m0 = mi * BM + q * 32;
       const int n0 = ni * BN;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-
-      // columns handled per TMA store: a 128-byte row for N-major output, 32 for M-major
-      constexpr int SC = OUT_M_MAJOR ? 32 : (128 / (int)sizeof(OutT));
-      constexpr int SUB = SC / 32;
-#pragma unroll 1
-      for (int c = 0; c < BN / SC; ++c) {
-        uint8_t* sb = my_buf + (nstore & 1) * EPI_BUF;
-        if (lane == 0) tma_store_wait_read<1>();  // the store that last used `sb` has drained
-        __syncwarp();
-#pragma unroll
-        for (int s = 0; s < SUB; ++s) {
-          uint32_t v[32];
-          const int col0 = c * SC + s * 32;
-          tmem_ld_x32(t_addr + col0, v);
-          tmem_ld_wait();
-          if (c == BN / SC - 1 && s == SUB - 1) {
-            // last read of this accumulator: hand it back to the MMA warp
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          }
-          if (g.beta != 0.f) {
-            const int row = m0 + lane;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = n0 + col0 + j;
-              if (row < g.M && col < g.N) {
-                const long long off = (long long)row * g.c_sm + (long long)col * g.c_sn;
-                if constexpr (INT_OUT) {
-                  v[j] = (uint32_t)((int)v[j] + reinterpret_cast<const int*>(g.C)[off]);
-                } else {
-                  float cin = load_c_as_float<OutT>(g.C, off);
-                  v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha + g.beta * cin);
-                }
-              }
-            }
-          } else if constexpr (!INT_OUT) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha);
-          }
-          if constexpr (OUT_M_MAJOR) {
-            // staging tile is [32 columns][32 rows], rows contiguous: conflict-free
-            if constexpr (INT_OUT) {
-              int* so = reinterpret_cast<int*>(sb);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) so[j * 32 + lane] = (int)v[j];
-            } else {
-              OutT* so = reinterpret_cast<OutT*>(sb);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) so[j * 32 + lane] = cvt_out<OutT>(__uint_as_float(v[j]));
-            }
-          } else {
-            // staging tile is [32 rows][128 bytes] in the 128-byte swizzle the store map expects
-            uint8_t* rowp = sb + lane * 128;
-            if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  OutT lo = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e]));
-                  OutT hi = cvt_out<OutT>(__uint_as_float(v[8 * j + 2 * e + 1]));
-                  w[e] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) |
-                         ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
-                }
-                const int chunk = s * 4 + j;
-                *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            }
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (OUT_M_MAJOR)
-            tma_store_2d(&tmD, sb, m0, n0 + c * SC);
-          else
-            tma_store_2d(&tmD, sb, n0 + c * SC, m0);
-          tma_store_commit();
-        }
-        ++nstore;
-      }
+      epilogue_tile<KIND, OutT, OUT_M_MAJOR, BN>(g, &tmD, t_addr, m0, n0, my_buf, nstore, lane, &acc_empty[buf], 0u);
     }
     if (lane == 0) tma_store_wait_all<0>();
   }
@@ -286,6 +301,179 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// The same GEMM on CTA pairs (tcgen05 cta_group::2).  A cluster of two CTAs owns a 256 x BN
+// output tile: each CTA holds its 128 rows of A and of the accumulator and HALF of the B tile
+// (BN/2 rows); the tensor cores of the pair read both halves of B.  Per 64-wide K block a
+// CTA therefore loads 16 KB + BN/2 * 128 B instead of 16 KB + BN * 128 B, which is what the
+// single-CTA kernel runs out of (its L2 -> SM operand feed).  Only the leader CTA (cluster
+// rank 0) issues MMAs.  Signalling across the pair:
+//   full[s]      (leader)   count 2: one arrive.expect_tx per CTA; the peer's TMA loads complete on
+//                           the leader's barrier (cp.async.bulk.tensor ... cta_group::2)
+//   empty[s]     (each CTA) tcgen05.commit by the leader, once to its own and once to the peer's barrier
+//   acc_full[b]  (each CTA) likewise
+//   acc_empty[b] (leader)   count 8: the four epilogue warps of both CTAs
+// No multicast is used anywhere.
+enum : int { SITE2_PROD_EMPTY = 111, SITE2_MMA_ACC = 112, SITE2_MMA_FULL = 113, SITE2_EPI_ACC = 114 };
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+  constexpr int BM = 128;              // rows per CTA; the pair covers 256
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int BK = 128 / ELEM;
+  constexpr int UMMA_K = 32 / ELEM;
+  constexpr int A_BYTES = BM * 128;
+  constexpr int B_BYTES = (BN / 2) * 128;  // this CTA's half of the B tile
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int EPI_BUF = 4096;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile N");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + 8 * EPI_BUF);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int num_tiles = g.m_tiles * g.n_tiles;  // m_tiles counts 256-row pair tiles here
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_holder, TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();  // both CTAs' barriers are initialised and both halves of the TMEM pair are allocated
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int mi, ni;
+        tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+        const int row_a = mi * 256 + (int)rank * BM;
+        const int row_b = ni * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE2_PROD_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          if (rank == 0) {
+            mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, row_a);
+            tma_load_2d(sa + A_BYTES, &tmB, &full[stage], kb * BK, row_b);
+          } else {
+            const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
+            mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, row_a);
+            tma_load_2d_pair(sa + A_BYTES, &tmB, leader_full, kb * BK, row_b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int lt = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++lt) {
+        const int buf = lt & 1;
+        const uint32_t aphase = (lt >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE2_MMA_ACC)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < g.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, g.status, SITE2_MMA_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k_sw128(sa);
+          const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            tc_mma_ss2<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t e_local = smem_u32(&empty[stage]);
+          tc_commit2(e_local);                  // frees this stage in the leader ...
+          tc_commit2(mapa_shared(e_local, 1));  // ... and in the peer
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          const uint32_t f_local = smem_u32(&acc_full[buf]);
+          tc_commit2(f_local);
+          tc_commit2(mapa_shared(f_local, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    uint8_t* my_buf = epi + (warp - 2) * 2 * EPI_BUF;
+    int nstore = 0;
+    int lt = 0;
+    for (int t = cluster_id; t < num_tiles; t += num_clusters, ++lt) {
+      int mi, ni;
+      tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+      const int buf = lt & 1;
+      const uint32_t aphase = (lt >> 1) & 1;
+      if (!mbar_wait(&acc_full[buf], aphase, g.status, SITE2_EPI_ACC)) break;
+      tc_fence_after_sync();
+      const int m0 = mi * 256 + (int)rank * BM + q * 32;
+      const int n0 = ni * BN;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      const uint32_t remote = rank == 0 ? 0u : mapa_shared(smem_u32(&acc_empty[buf]), 0);
+      epilogue_tile<KIND, OutT, OUT_M_MAJOR, BN>(g, &tmD, t_addr, m0, n0, my_buf, nstore, lane, &acc_empty[buf], remote);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*reinterpret_cast<volatile int*>(g.status) != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  // neither CTA may leave while its partner can still signal its barriers or read its operands
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------- host side
 
 template <int BN>
@@ -300,7 +488,7 @@ static int launch_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMa
   static_assert(STAGES >= 3, "pipeline too shallow");
   constexpr int SMEM = STAGES * (128 * 128 + BN * 128) + 8 * 4096 + 256 + 1024;
   auto kern = gemm_tcgen05_kernel<KIND, OutT, OUT_M_MAJOR, BN, STAGES>;
-  MOYE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+  if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
   const int tiles = args.m_tiles * args.n_tiles;
   const int grid = tiles < h->num_sms ? tiles : h->num_sms;
   kern<<<grid, 192, SMEM, stream>>>(ta, tb, td, args);
@@ -324,6 +512,55 @@ static int launch_major(bool m_major, int bn, moye_b200_ctx* h, const CUtensorMa
                         const CUtensorMap& td, const GemmArgs& args, cudaStream_t stream) {
   return m_major ? launch_bn<KIND, OutT, true>(bn, h, ta, tb, td, args, stream)
                  : launch_bn<KIND, OutT, false>(bn, h, ta, tb, td, args, stream);
+}
+
+
+template <int BN>
+constexpr int stages_for_pair() {
+  return (227 * 1024 - 8 * 4096 - 1024 - 256) / (128 * 128 + (BN / 2) * 128);
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN>
+static int launch_pair_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                            const GemmArgs& args, cudaStream_t stream) {
+  constexpr int STAGES = stages_for_pair<BN>();
+  constexpr int SMEM = STAGES * (128 * 128 + (BN / 2) * 128) + 8 * 4096 + 256 + 1024;
+  auto kern = gemm_tcgen05_2cta_kernel<KIND, OutT, OUT_M_MAJOR, BN, STAGES>;
+  if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
+  const int tiles = args.m_tiles * args.n_tiles;
+  int clusters = h->num_sms / 2;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MOYE_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, td, args));
+  return MOYE_OK;
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR>
+static int launch_pair_bn(int bn, moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb,
+                          const CUtensorMap& td, const GemmArgs& args, cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_pair_inst<KIND, OutT, OUT_M_MAJOR, 256>(h, ta, tb, td, args, stream);
+    case 128: return launch_pair_inst<KIND, OutT, OUT_M_MAJOR, 128>(h, ta, tb, td, args, stream);
+    default: MOYE_FAIL(MOYE_ERR_INVALID_ARG, "CTA pairs take tile_n 128 or 256 (got %d)", bn);
+  }
+}
+
+template <int KIND, typename OutT>
+static int launch_pair_major(bool m_major, int bn, moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb,
+                             const CUtensorMap& td, const GemmArgs& args, cudaStream_t stream) {
+  return m_major ? launch_pair_bn<KIND, OutT, true>(bn, h, ta, tb, td, args, stream)
+                 : launch_pair_bn<KIND, OutT, false>(bn, h, ta, tb, td, args, stream);
 }
 
 int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
@@ -383,12 +620,15 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
 
   int bn = p.tile_n;
   if (bn == 0) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const bool pair = p.path == 3 || (p.path == 0 && M > 128 && bn >= 128);
+  if (pair && bn < 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "CTA pairs take tile_n 128 or 256 (got %d)", bn);
 
   const int eb = dtype_bytes(A->dtype);
   const int bk = 128 / eb;
   CUtensorMap ta, tb, td;
   if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * eb, bk, 128, true)) return rc;
-  if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, bn, true)) return rc;
+  if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, pair ? bn / 2 : bn, true))
+    return rc;
   const int ob = dtype_bytes(out);
   if (m_major) {
     if (int rc = make_tmap_2d(h, &td, D->ptr, out, M, N, (uint64_t)D->stride[1] * ob, 32, 32, false)) return rc;
@@ -398,11 +638,12 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
 
   GemmArgs a;
   a.M = (int)M; a.N = (int)N; a.K = (int)K;
-  a.m_tiles = (int)((M + 127) / 128);
+  a.m_tiles = pair ? (int)((M + 255) / 256) : (int)((M + 127) / 128);
   a.n_tiles = (int)((N + bn - 1) / bn);
   a.k_blocks = (int)((K + bk - 1) / bk);
-  a.group_m = 16;
-  a.idesc = (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  a.group_m = pair ? 8 : 16;
+  a.idesc = (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(bn >> 3) << 17) |
+            ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
   a.alpha = alpha;
   a.beta = p.beta;
   a.C = (p.beta != 0.f) ? C->ptr : nullptr;
@@ -410,6 +651,18 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   a.c_sn = (p.beta != 0.f) ? C->stride[1] : 0;
   a.status = h->d_status;
 
+  if (pair) {
+    if (kind == KIND_F16) {
+      if (out == MOYE_F32) return launch_pair_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);
+      if (out == MOYE_F16) return launch_pair_major<KIND_F16, __half>(m_major, bn, h, ta, tb, td, a, stream);
+      return launch_pair_major<KIND_F16, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+    } else if (kind == KIND_I8) {
+      return launch_pair_major<KIND_I8, int>(m_major, bn, h, ta, tb, td, a, stream);
+    } else {
+      if (out == MOYE_F32) return launch_pair_major<KIND_F8, float>(m_major, bn, h, ta, tb, td, a, stream);
+      return launch_pair_major<KIND_F8, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+    }
+  }
   if (kind == KIND_F16) {
     if (out == MOYE_F32) return launch_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);
     if (out == MOYE_F16) return launch_major<KIND_F16, __half>(m_major, bn, h, ta, tb, td, a, stream);

@@ -85,15 +85,15 @@ def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
     for m_major in (False, True):
         if m_major and (M * torch.empty(0, dtype=out_dtype).element_size()) % 16:
             continue
-        for tile_n in (0, 64, 128, 256):
+        for path, tile_n in ((1, 0), (1, 64), (1, 128), (1, 256), (3, 128), (3, 256), (0, 0)):
             C = out_tensor(M, N, out_dtype, dev, m_major)
-            mb.matmul(A, B, C, tile_n=tile_n, path=1)
+            mb.matmul(A, B, C, tile_n=tile_n, path=path)  # 1 = single CTAs, 3 = CTA pairs, 0 = library's choice
             mb.synchronize_status(dev)
             got = C.float().cpu().numpy() if kind != "s8" else C.cpu().numpy()
             if kind == "s8":
-                assert np.array_equal(got, ref), (m_major, tile_n)
+                assert np.array_equal(got, ref), (m_major, path, tile_n)
             else:
-                assert ho.max_rel_err(got, ref) <= TOL[kind], (m_major, tile_n)
+                assert ho.max_rel_err(got, ref) <= TOL[kind], (m_major, path, tile_n)
 
 
 def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
@@ -236,3 +236,27 @@ def test_gemm_argument_errors(mb, dev):
     D32 = T(out.data_ptr(), mb._lib.S32, [128, 128], [128, 1])
     assert call(D=D32, A=A8, B=A8, p=mb._lib.GemmParams(2.0, 0.0, 1.0, 1.0, 0, 0, 0, 0)) == -1  # s8 path is exact
     mb.synchronize_status(dev)
+
+
+def test_prepared_plans_match_direct_calls(mb, ho, dev):
+    """plan_gemm / plan_copy marshal the arguments once; repeated launches must equal the direct call."""
+    M, N, K = 512, 384, 256
+    a, b, A, B, dt = operands(ho, "f16", M, N, K, dev, (3, 4))
+    want = torch.zeros(M, N, device=dev)
+    mb.matmul(A, B, want)
+    got = torch.zeros(M, N, device=dev)
+    plan = mb.plan_gemm(mb.make_tiled_mma(mb.sm100_mma_op("F16", 256)), got, A, B, None)
+    for _ in range(3):
+        got.zero_()
+        plan()
+        mb.synchronize_status(dev)
+        assert torch.equal(got, want)
+    src = torch.rand(96, 1024, device=dev).half()
+    dst = torch.zeros_like(src)
+    lay = mb.make_layout((1024, 96))
+    cp = mb.plan_copy(mb.make_tma_tiled_copy(mb._lib.F16), mb.MoYeArray(dst, lay), mb.MoYeArray(src, lay))
+    cp(mb.current_stream_ptr(dev))
+    mb.synchronize_status(dev)
+    assert torch.equal(src, dst)
+    with pytest.raises(mb.MoyeError):
+        mb.plan_copy(mb.MoYeArray(dst, mb.make_layout((96, 1024), (1024, 1))), mb.MoYeArray(src, lay))
