@@ -42,6 +42,8 @@ WORKLOADS = {
     "gemm_e4m3_16384x8192x8192": ("e4m3", 16384, 8192, 8192, "bf16"),
     "decode_bf16_16x28672x8192": ("bf16", 16, 28672, 8192, "bf16"),
     "copy_f16_8192": ("copy", 8192, 8192, 0, "f16"),
+    # the storage of the reference's examples/gemm.jl: A (M,K), B (N,K), C (M,N) all column-major
+    "gemm_f16_8192_colmajor": ("f16", 8192, 8192, 8192, "f32"),
     # a smaller case of the same dense kernel (224 MB of operands + output, still larger than L2),
     # sized for multi-pass profiler captures
     "gemm_f16_4096x8192x4096": ("f16", 4096, 8192, 4096, "f32"),
@@ -116,7 +118,7 @@ def flops_of(kind, M, N, K):
     return 2.0 * M * N * K
 
 
-def make_operands(torch, kind, M, N, K, out, dev, seed):
+def make_operands(torch, kind, M, N, K, out, dev, seed, colmajor=False):
     g = torch.Generator(device=dev).manual_seed(seed)
     if kind == "f16":
         A = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).half()
@@ -132,6 +134,8 @@ def make_operands(torch, kind, M, N, K, out, dev, seed):
         B = torch.randn(N, K, device=dev, generator=g).clamp(-448, 448).to(torch.float8_e4m3fn)
     odt = {"f32": torch.float32, "s32": torch.int32, "bf16": torch.bfloat16, "f16": torch.float16}[out]
     C = torch.zeros(M, N, device=dev, dtype=odt)
+    if colmajor:
+        A, B, C = A.t().contiguous().t(), B.t().contiguous().t(), C.t().contiguous().t()
     return A, B, C
 
 
@@ -220,7 +224,8 @@ def run_reference_arm(args):
 
 def workload_config(name, gpus):
     kind, M, N, K, out = WORKLOADS[name]
-    return {"workload": name, "M_per_gpu": M, "N": N, "K": K, "global_M": M * gpus, "layout": "A,B K-major (TN); D row-major",
+    return {"workload": name, "M_per_gpu": M, "N": N, "K": K, "global_M": M * gpus,
+            "layout": "A,B,D column-major (MN-major, as examples/gemm.jl)" if name.endswith("_colmajor") else "A,B K-major (TN); D row-major",
             "in": kind, "out": out, "sharding": f"M-sharded x{gpus}, B replicated, no collective",
             "l2": "operands+output exceed the 126 MB L2 (no flush needed)" if M * K + N * K > 64e6 else "rotating buffers"}
 
@@ -260,7 +265,7 @@ def run_ours(args):
     if kind == "copy":
         return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier)
 
-    A, B, C = make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank)
+    A, B, C = make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank, colmajor=name.endswith("_colmajor"))
     kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
     mA, mB, mC = mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(C)
     plan = mb.plan_gemm(mC, mA, mB, None, **kw)   # the argument marshalling of gemm_ done once
@@ -370,11 +375,12 @@ def extras(mb, torch, dev, peaks):
     """The other configurations, each timed alone for a few launches (reported beside the headline)."""
     out = {}
     stream = torch.cuda.current_stream()
-    for name in ("gemm_f16_4096", "gemm_bf16_8192", "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192",
-                 "decode_bf16_16x28672x8192"):
+    for name in ("gemm_f16_4096", "gemm_f16_8192_colmajor", "gemm_bf16_8192", "gemm_s8_16384x8192x8192",
+                 "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192"):
         kind, M, N, K, o = WORKLOADS[name]
         nset = 3 if M <= 32 else 1  # rotate weight buffers for the HBM-bound decode shape
-        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i) for i in range(nset)]
+        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i, colmajor=name.endswith("_colmajor"))
+                for i in range(nset)]
         kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
         plans = [mb.plan_gemm(c, a, b, None, **kw) for a, b, c in sets]
         sp = mb.current_stream_ptr(dev)

@@ -29,6 +29,7 @@ struct GemmArgs {
   const void* C;
   long long c_sm, c_sn;  // strides of C in elements
   int* status;
+  int a_mn, b_mn;  // 1: the operand is MN-major (stride 1 along M / N) instead of K-major
 };
 
 // Wait-site codes reported through the status word.
@@ -60,6 +61,35 @@ __device__ __forceinline__ float load_c_as_float(const void* C, long long off) {
   return static_cast<float>(reinterpret_cast<const OutT*>(C)[off]);
 }
 
+
+// One operand tile of `rows` x BK into shared memory at `dst`.  K-major: one box {BK, rows}.
+// MN-major: the tile is split into chunks of 128 bytes along MN, each a box {128 B, BK rows}.
+template <int ELEM, int BK>
+__device__ __forceinline__ void load_operand(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int mn, int row0,
+                                             int rows, int kb) {
+  if (!mn) {
+    tma_load_2d(dst, tm, bar, kb * BK, row0);
+  } else {
+    constexpr int CH = 128 / ELEM;  // elements per 128-byte chunk
+    for (int c = 0; c * CH < rows; ++c) tma_load_2d(dst + c * (BK * 128), tm, bar, row0 + c * CH, kb * BK);
+  }
+}
+template <int ELEM, int BK>
+__device__ __forceinline__ void load_operand_pair(uint8_t* dst, const CUtensorMap* tm, uint32_t bar, int mn, int row0,
+                                                  int rows, int kb) {
+  if (!mn) {
+    tma_load_2d_pair(dst, tm, bar, kb * BK, row0);
+  } else {
+    constexpr int CH = 128 / ELEM;
+    for (int c = 0; c * CH < rows; ++c) tma_load_2d_pair(dst + c * (BK * 128), tm, bar, row0 + c * CH, kb * BK);
+  }
+}
+// Descriptor of the k-th UMMA_K slice of an operand tile, and what advancing k means per majorness.
+template <int BK, int UMMA_K>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr, int mn, int k) {
+  if (!mn) return umma_desc_k_sw128(smem_addr) + 2 * k;                       // +32 bytes inside the swizzled row
+  return umma_desc_mn_sw128(smem_addr + k * (UMMA_K * 128), BK * 128);        // UMMA_K rows of 128 bytes further
+}
 
 // Epilogue of one accumulator tile for one warp: its 32 TMEM lanes x BN columns go
 // TMEM -> registers -> (alpha, beta, convert) -> staging tile in shared memory -> TMA store.
@@ -229,8 +259,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_PROD_EMPTY)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          tma_load_2d(sa, &tmA, &full[stage], kb * BK, mi * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, &full[stage], kb * BK, ni * BN);
+          load_operand<ELEM, BK>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb);
+          load_operand<ELEM, BK>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -252,13 +282,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!mbar_wait(&full[stage], phase, g.status, SITE_MMA_FULL)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint64_t adesc = umma_desc_k_sw128(sa);
-          const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advancing K by one instruction = 32 bytes inside the swizzled row = +2 in the
-            // (address >> 4) field of the descriptor
-            tc_mma_ss<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_ss<KIND>(d_tmem, operand_desc<BK, UMMA_K>(sa, g.a_mn, k),
+                            operand_desc<BK, UMMA_K>(sa + A_BYTES, g.b_mn, k), g.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -390,13 +417,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint8_t* sa = smem + stage * STAGE_BYTES;
           if (rank == 0) {
             mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-            tma_load_2d(sa, &tmA, &full[stage], kb * BK, row_a);
-            tma_load_2d(sa + A_BYTES, &tmB, &full[stage], kb * BK, row_b);
+            load_operand<ELEM, BK>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
+            load_operand<ELEM, BK>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, BN / 2, kb);
           } else {
             const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
             mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);
-            tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, row_a);
-            tma_load_2d_pair(sa + A_BYTES, &tmB, leader_full, kb * BK, row_b);
+            load_operand_pair<ELEM, BK>(sa, &tmA, leader_full, g.a_mn, row_a, BM, kb);
+            load_operand_pair<ELEM, BK>(sa + A_BYTES, &tmB, leader_full, g.b_mn, row_b, BN / 2, kb);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -419,11 +446,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (!mbar_wait(&full[stage], phase, g.status, SITE2_MMA_FULL)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint64_t adesc = umma_desc_k_sw128(sa);
-          const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            tc_mma_ss2<KIND>(d_tmem, adesc + 2 * k, bdesc + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_ss2<KIND>(d_tmem, operand_desc<BK, UMMA_K>(sa, g.a_mn, k),
+                             operand_desc<BK, UMMA_K>(sa + A_BYTES, g.b_mn, k), g.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           const uint32_t e_local = smem_u32(&empty[stage]);
           tc_commit2(e_local);                  // frees this stage in the leader ...
@@ -596,9 +622,14 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
                       (A->dtype == MOYE_S8 && out == MOYE_S32) ||
                       (A->dtype == MOYE_E4M3 && (out == MOYE_BF16 || out == MOYE_F32));
   if (!out_ok) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
-  if (A->stride[1] != 1 || B->stride[1] != 1)
-    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B must be K-major (stride 1 along K); got %lld and %lld",
-              (long long)A->stride[1], (long long)B->stride[1]);
+  // K-major (stride 1 along K) or MN-major (stride 1 along M / N, MoYe's column-major default)
+  const bool a_mn = A->stride[1] != 1 || (K == 1 && A->stride[0] == 1 && M > 1);
+  const bool b_mn = B->stride[1] != 1 || (K == 1 && B->stride[0] == 1 && N > 1);
+  if ((a_mn || b_mn) && kind != KIND_F16)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "8-bit operands must be K-major (MN-major tiles are built for 16-bit types)");
+  if ((a_mn && A->stride[0] != 1) || (b_mn && B->stride[0] != 1))
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B need a unit stride along K or along M / N; got A (%lld,%lld), B (%lld,%lld)",
+              (long long)A->stride[0], (long long)A->stride[1], (long long)B->stride[0], (long long)B->stride[1]);
   bool m_major;
   if (D->stride[0] == 1 && (D->stride[1] != 1 || N == 1)) m_major = true;
   else if (D->stride[1] == 1) m_major = false;
@@ -615,7 +646,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
       MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "C must match D in shape and dtype");
   }
 
-  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512))
+  if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
+  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512 && !a_mn && !b_mn))
     return launch_gemm_skinny(h, D, A, B, &p, stream);
 
   int bn = p.tile_n;
@@ -626,9 +658,18 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   const int eb = dtype_bytes(A->dtype);
   const int bk = 128 / eb;
   CUtensorMap ta, tb, td;
-  if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * eb, bk, 128, true)) return rc;
-  if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, pair ? bn / 2 : bn, true))
-    return rc;
+  const int ch = 128 / eb;  // elements in one 128-byte chunk
+  if (a_mn) {
+    if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, M, K, (uint64_t)A->stride[1] * eb, ch, bk, true)) return rc;
+  } else {
+    if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * eb, bk, 128, true)) return rc;
+  }
+  if (b_mn) {
+    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, N, K, (uint64_t)B->stride[1] * eb, ch, bk, true)) return rc;
+  } else {
+    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, pair ? bn / 2 : bn, true))
+      return rc;
+  }
   const int ob = dtype_bytes(out);
   if (m_major) {
     if (int rc = make_tmap_2d(h, &td, D->ptr, out, M, N, (uint64_t)D->stride[1] * ob, 32, 32, false)) return rc;
@@ -642,8 +683,10 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   a.n_tiles = (int)((N + bn - 1) / bn);
   a.k_blocks = (int)((K + bk - 1) / bk);
   a.group_m = pair ? 8 : 16;
-  a.idesc = (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(bn >> 3) << 17) |
-            ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
+  a.idesc = (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
+  a.a_mn = a_mn ? 1 : 0;
+  a.b_mn = b_mn ? 1 : 0;
   a.alpha = alpha;
   a.beta = p.beta;
   a.C = (p.beta != 0.f) ? C->ptr : nullptr;

@@ -285,4 +285,18 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_byte_addr) {
   return d;
 }
 
+// The same for an MN-major operand tile (the M or N index is the contiguous one, as in MoYe's
+// column-major arrays): the tile is stored as chunks of 64 x 16-bit (128 bytes) along MN; inside a
+// chunk consecutive K rows are 128 bytes apart and 8 of them form one 1024-byte swizzle atom
+// (stride byte offset), successive chunks are `chunk_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_byte_addr, uint32_t chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_byte_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((chunk_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 }  // namespace moye

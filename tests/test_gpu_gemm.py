@@ -96,6 +96,49 @@ def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
                 assert ho.max_rel_err(got, ref) <= TOL[kind], (m_major, path, tile_n)
 
 
+def col_major(t):
+    """Same values, stride 1 along the first mode (MoYe's column-major default)."""
+    return t.t().contiguous().t()
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 520, 1008), (136, 72, 4096), (2048, 1024, 512)])
+def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
+    """A and / or B stored column-major, i.e. MN-major as in reference examples/gemm.jl:92-93
+    (A = randn(M, K), B = randn(N, K) in Julia), on both dense kernels."""
+    a, b, A, B, dt = operands(ho, kind, M, N, K, dev, (3, 4))
+    ref = ho.gemm_samples(a, b, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    for a_mn, b_mn in ((True, True), (True, False), (False, True)):
+        Ax = col_major(A) if a_mn else A
+        Bx = col_major(B) if b_mn else B
+        assert Ax.stride() == ((1, M) if a_mn else (K, 1))
+        for path in (1, 3):
+            for m_major in (False, True):
+                C = out_tensor(M, N, torch.float32, dev, m_major)
+                mb.matmul(Ax, Bx, C, path=path)
+                mb.synchronize_status(dev)
+                assert ho.max_rel_err(C.cpu().numpy(), ref) <= TOL[kind], (a_mn, b_mn, path, m_major)
+
+
+def test_examples_gemm_jl_storage(mb, ho, dev):
+    """The reference example end to end in its own storage: column-major A (M,K), B (N,K), C (M,N)
+    built as MoYeArrays over flat buffers, C = A * B' (reference examples/gemm.jl:66-100)."""
+    M, N, K = 2048, 2048, 256
+    a_bits, b_bits = ho.uniform_pm1_f16_bits(3, (M * K,)), ho.uniform_pm1_f16_bits(4, (N * K,))   # column-major buffers
+    A = mb.MoYeArray(dev_bits(a_bits, torch.float16, (M * K,), dev), mb.make_layout((M, K)))
+    B = mb.MoYeArray(dev_bits(b_bits, torch.float16, (N * K,), dev), mb.make_layout((N, K)))
+    Cbuf = torch.zeros(M * N, device=dev)
+    C = mb.MoYeArray(Cbuf, mb.make_layout((M, N)))
+    mb.matmul(A, B, C)
+    mb.synchronize_status(dev)
+    a32 = ho.half_to_float(a_bits)
+    b32 = ho.half_to_float(b_bits)
+    rows = np.arange(0, M, 16)
+    want = np.stack([ho.gemm_f32(a32[r::M].copy(), (0, 1), b32, (1, N), 1, N, K, c_strides=(N, 1)) for r in rows])
+    got = Cbuf.view(N, M).t()[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    assert ho.max_rel_err(got, want) <= 1e-2
+
+
 def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
     M, N, K = 256, 384, 512
     a, b, A, B, dt = operands(ho, "f16", M, N, K, dev, (3, 4))
@@ -220,7 +263,8 @@ def test_gemm_argument_errors(mb, dev):
                                   ctypes.byref(C) if C is not None else None, ctypes.byref(p), st)
 
     assert call() == 0
-    assert call(A=T(buf.data_ptr(), F16, [128, 64], [1, 128])) == -3                  # A not K-major
+    assert call(A=T(buf.data_ptr(), F16, [128, 64], [1, 128])) == 0                   # A column-major (MN-major) is fine
+    assert call(A=T(buf.data_ptr(), F16, [128, 64], [2, 256])) == -3                  # no unit stride at all
     assert call(A=T(buf.data_ptr(), F16, [128, 60], [60, 1]), B=T(buf.data_ptr(), F16, [128, 60], [60, 1])) == -5
     assert call(A=T(buf.data_ptr() + 2, F16, [128, 64], [64, 1])) == -5               # misaligned base
     assert call(B=T(buf.data_ptr(), F16, [128, 32], [32, 1])) == -4                   # K mismatch
@@ -235,6 +279,7 @@ def test_gemm_argument_errors(mb, dev):
     A8 = T(buf.data_ptr(), mb._lib.S8, [128, 64], [64, 1])
     D32 = T(out.data_ptr(), mb._lib.S32, [128, 128], [128, 1])
     assert call(D=D32, A=A8, B=A8, p=mb._lib.GemmParams(2.0, 0.0, 1.0, 1.0, 0, 0, 0, 0)) == -1  # s8 path is exact
+    assert call(D=D32, A=T(buf.data_ptr(), mb._lib.S8, [128, 64], [1, 128]), B=A8) == -3   # 8-bit operands: K-major only
     mb.synchronize_status(dev)
 
 
