@@ -30,8 +30,10 @@ sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM traffic of one launch of the 8192^3 fp16 GEMM kernel (dram__bytes_read.sum +
-# dram__bytes_write.sum from the ncu capture summarised under profiles/); None until captured.
-NCU_TRAFFIC_BYTES = {"gemm_f16_8192": None}
+# dram__bytes_write.sum from the ncu captures summarised under profiles/), bytes per launch.
+NCU_TRAFFIC_BYTES = {"gemm_f16_8192": 1.09e9 + 0.2515e9,       # profiles/gemm_tcgen05_2cta_f16_8192_dram_traffic.txt
+                     "decode_bf16_16x28672x8192": 471.24e6 + 6.1e6,  # profiles/gemm_skinny_bf16_16x28672x8192.txt
+                     "gemm_f16_4096x8192x4096": 179.6e6 + 100.5e6}
 
 WORKLOADS = {
     # name: (kind, M, N, K, out)
@@ -297,23 +299,21 @@ def run_ours(args):
     value = total_flops / (ms_max * 1e-3) / 1e12
     bytes_bound = kind == "bf16" and M <= 32
 
-    # end to end: pinned host operands -> device -> GEMM -> host, every step
+    # end to end: pinned host operands -> device -> GEMM -> pinned host result, every step, through the
+    # package's host pipeline (copies and kernel on three streams over two device buffer sets)
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
-    hC = torch.empty(C.shape, dtype=C.dtype).pin_memory()
-    e2e_steps = max(1, min(args.steps, 10))
-
-    def e2e_step():
-        A.copy_(hA, non_blocking=True)
-        B.copy_(hB, non_blocking=True)
-        mb.matmul(mA, mB, mC, **kw)
-        hC.copy_(C, non_blocking=True)
-
-    for _ in range(2):
-        e2e_step()
+    hC = [torch.empty(C.shape, dtype=C.dtype).pin_memory() for _ in range(2)]
+    e2e_steps = max(2, min(args.steps, 12))
+    pipe = mb.HostGemmPipeline(M, N, K, A.dtype, C.dtype, dev, depth=2, **kw)
+    for i in range(3):
+        pipe.submit(hA, hB, hC[i % 2])
+    pipe.join()
     barrier()
     e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
+    pipe.start_after(e0)
+    for i in range(e2e_steps):
+        pipe.submit(hA, hB, hC[i % 2])
+    pipe.join(stream)
     e1.record(stream)
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
@@ -321,6 +321,21 @@ def run_ours(args):
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
+    # the same step with its three phases back to back on one stream (no overlap), for reference
+    def serial_step():
+        A.copy_(hA, non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        plan(stream_ptr)
+        hC[0].copy_(C, non_blocking=True)
+
+    serial_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(4):
+        serial_step()
+    e1.record(stream)
+    barrier()
+    e2e_serial_ms = e0.elapsed_time(e1) / 4
     h2d = A.numel() * A.element_size() + B.numel() * B.element_size()
     d2h = C.numel() * C.element_size()
 
@@ -348,7 +363,9 @@ def run_ours(args):
                   "e4m3": "e4m3 (f32 accumulate)"}[kind],
         "data": "synthetic", "config": workload_config(name, world), "clocks": clocks, "gpu_launches": args.steps,
         "e2e": {"value": e2e_val, "unit": munit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "how": "HostGemmPipeline: H2D, GEMM, D2H on three streams, two device buffer sets; every step copies its own operands in and its result out",
+                "serial_ms_per_step": e2e_serial_ms},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_kind}, of {peak_src}",
                      "kernel": "gemm_tcgen05_2cta_kernel" if not bytes_bound else "gemm_skinny_kernel",

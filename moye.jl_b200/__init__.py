@@ -12,6 +12,7 @@ from .array import *  # noqa: F401,F403
 from .atom import *  # noqa: F401,F403
 from .algorithm import *  # noqa: F401,F403
 from .sharding import *  # noqa: F401,F403
+from .host_pipeline import *  # noqa: F401,F403
 from ._lib import MoyeError
 
 __version__ = "0.1.0"

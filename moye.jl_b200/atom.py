@@ -27,7 +27,7 @@ __all__ = [
     "MMAOp", "CopyOp", "UniversalFMA", "UniversalCopy", "CPOP_ASYNC_CACHEALWAYS", "CPOP_TMA_LOAD_SW128",
     "CPOP_TMA_STORE", "MMAAtom", "TiledMMA", "ThrMMA", "make_tiled_mma", "CopyAtom", "TiledCopy", "ThrCopy",
     "make_tiled_copy", "make_tma_tiled_copy", "make_tiled_copy_A", "make_tiled_copy_B", "make_tiled_copy_C", "MMA_OPS", "mma_op",
-    "sm100_mma_op", "DTYPE_BITS",
+    "sm100_mma_op", "DTYPE_BITS", "LDSM_OPS", "ldsm_op",
 ]
 
 DTYPE_BITS = {_lib.F32: 32, _lib.F16: 16, _lib.BF16: 16, _lib.S8: 8, _lib.U8: 8, _lib.E4M3: 8, _lib.S32: 32,
@@ -275,6 +275,32 @@ def CPOP_ASYNC_CACHEALWAYS(bits):
         raise ValueError("cp.async moves 4, 8 or 16 bytes")
     return CopyOp(f"CPOP_ASYNC_CACHEALWAYS{{{bits}b}}", L(1), L((1, bits)), L((1, bits)),
                   mode=_lib.COPY_UNIVERSAL128 if bits == 128 else None)
+
+
+def _ldsm(name, src, dst):
+    return CopyOp(name, L(32), src, dst, dst)
+
+
+# ldmatrix ops: 32 threads move 1 / 2 / 4 8x8 b16 matrices from shared memory to registers, optionally
+# transposed.  Bit-level (thread, bit) layouts as in reference src/traits/ldmatrix.jl:1-41 (ops:
+# src/arch/copy/ldmatrix.jl:18-48).  tcgen05 reads its operands straight from shared-memory descriptors,
+# so the B200 kernels do not issue ldmatrix; the ops exist so that TiledCopy objects built on them
+# (reference test/copy.jl:152-157, docs/src/manual/tensor_core.md) partition exactly as in MoYe.
+LDSM_OPS = {
+    "LDSM_U32x1_N": _ldsm("LDSM_U32x1_N", L(((8, 4), 128), ((128, 0), 1)), L((32, 32), (32, 1))),
+    "LDSM_U32x2_N": _ldsm("LDSM_U32x2_N", L(((16, 2), 128), ((128, 0), 1)), L((32, (32, 2)), (32, (1, 1024)))),
+    "LDSM_U32x4_N": _ldsm("LDSM_U32x4_N", L((32, 128), (128, 1)), L((32, (32, 4)), (32, (1, 1024)))),
+    "LDSM_U16x2_T": _ldsm("LDSM_U16x2_T", L(((8, 4), 128), ((128, 0), 1)),
+                          L(((4, 8), (16, 2)), ((256, 16), (1, 128)))),
+    "LDSM_U16x4_T": _ldsm("LDSM_U16x4_T", L(((16, 2), 128), ((128, 0), 1)),
+                          L(((4, 8), (16, 2, 2)), ((256, 16), (1, 128, 1024)))),
+    "LDSM_U16x8_T": _ldsm("LDSM_U16x8_T", L((32, 128), (128, 1)),
+                          L(((4, 8), (16, 2, 4)), ((256, 16), (1, 128, 1024)))),
+}
+
+
+def ldsm_op(name):
+    return LDSM_OPS[name]
 
 
 def CPOP_TMA_LOAD_SW128(tile_bits):

@@ -305,3 +305,24 @@ def test_prepared_plans_match_direct_calls(mb, ho, dev):
     assert torch.equal(src, dst)
     with pytest.raises(mb.MoyeError):
         mb.plan_copy(mb.MoYeArray(dst, mb.make_layout((96, 1024), (1024, 1))), mb.MoYeArray(src, lay))
+
+
+def test_host_pipeline_steps_are_each_correct(mb, ho, dev):
+    """Five host-to-host steps with different operands through the three-stream pipeline."""
+    M, N, K = 256, 384, 512
+    pipe = mb.HostGemmPipeline(M, N, K, torch.float16, torch.float32, dev, depth=2)
+    hosts, outs, refs = [], [], []
+    for i in range(5):
+        a, b = ho.uniform_pm1_f16_bits(30 + i, (M * K,)), ho.uniform_pm1_f16_bits(40 + i, (N * K,))
+        hA = torch.from_numpy(a.view(np.int16)).view(torch.float16).view(M, K).pin_memory()
+        hB = torch.from_numpy(b.view(np.int16)).view(torch.float16).view(N, K).pin_memory()
+        hC = torch.zeros(M, N).pin_memory()
+        hosts.append((hA, hB))
+        outs.append(hC)
+        refs.append(ho.gemm_samples(a, b, ho.F16, M, N, K, np.arange(0, M, 5, dtype=np.int32), threads=NTHREADS))
+        pipe.submit(hA, hB, hC)
+    pipe.join()
+    torch.cuda.synchronize()
+    mb.synchronize_status(dev)
+    for hC, ref in zip(outs, refs):
+        assert ho.max_rel_err(hC.numpy()[::5], ref) <= 1e-2

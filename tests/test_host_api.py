@@ -252,6 +252,28 @@ def test_tiled_copy_goldens(mb):
         mb.TiledCopy(mb.CopyAtom(mb.UniversalCopy(128), mb._lib.F16), mb.make_layout((256, 4)), (128, 8))
 
 
+def test_ldmatrix_atoms_construct_and_tile(mb):
+    # reference test/copy.jl:152-157: the three non-transposed ldmatrix atoms tile (16,2) x (2,4) threads/values;
+    # reference test/device/tiled_copy.jl:60-89 uses the transposed ones on u16
+    for name, nsrc, ndst in (("LDSM_U32x1_N", 8, 2), ("LDSM_U32x2_N", 8, 4), ("LDSM_U32x4_N", 8, 8),
+                             ("LDSM_U16x2_T", 8, 2), ("LDSM_U16x4_T", 8, 4), ("LDSM_U16x8_T", 8, 8)):
+        atom = mb.CopyAtom(mb.ldsm_op(name), mb._lib.U16)
+        assert mb.size(atom.thr_id) == 32
+        assert atom.num_val_src == nsrc and atom.num_val_dst == ndst
+    for name in ("LDSM_U32x1_N", "LDSM_U32x2_N", "LDSM_U32x4_N"):
+        tc = mb.make_tiled_copy(mb.CopyAtom(mb.ldsm_op(name), mb._lib.U16), mb.make_layout((16, 2)), mb.make_layout((2, 4)))
+        assert len(tc) == 32 and tc.tiler_mn == (32, 8)
+    # every destination value of a 32x8 u16 tile is produced exactly once by an x4 atom over 32 threads
+    tc = mb.make_tiled_copy(mb.CopyAtom(mb.ldsm_op("LDSM_U32x4_N"), mb._lib.U16), mb.make_layout((32, 1)), mb.make_layout((1, 8)))
+    tile = mb.MoYeArray(torch.arange(1, 257, dtype=torch.int16), mb.make_layout((32, 8)))
+    seen = torch.zeros(256, dtype=torch.int32)
+    for tid in range(1, 33):
+        d = tc.get_slice(tid).partition_D(tile)
+        for i in range(1, len(d) + 1):
+            seen[d[i] - 1] += 1
+    assert bool((seen == 1).all())
+
+
 def test_host_operands_are_rejected(mb):
     a = mb.MoYeArray(torch.zeros(64, 64, dtype=torch.float16))
     c = mb.MoYeArray(torch.zeros(64, 64))
