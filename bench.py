@@ -368,7 +368,7 @@ def run_ours(args):
                 "serial_ms_per_step": e2e_serial_ms},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_kind}, of {peak_src}",
-                     "kernel": "gemm_tcgen05_2cta_kernel" if not bytes_bound else "gemm_skinny_kernel",
+                     "kernel": "gemm_tcgen05_2cta_wide_kernel" if not bytes_bound else "gemm_skinny_kernel",
                      "kernel_ms": ms},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -92,7 +92,8 @@ typedef struct {
   int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128 */
   int32_t split_k;               /* skinny path only: 0 = auto */
   int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel,
-                                    3 dense kernel on CTA pairs (cta_group::2) */
+                                    3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
+                                    4 CTA pairs on 256 x 512 tiles */
   int32_t flags;                 /* reserved, must be 0 */
 } moye_gemm_params_t;
 

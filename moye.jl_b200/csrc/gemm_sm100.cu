@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -64,38 +66,51 @@ __device__ __forceinline__ float load_c_as_float(const void* C, long long off) {
 
 // One operand tile of `rows` x BK into shared memory at `dst`.  K-major: one box {BK, rows}.
 // MN-major: the tile is split into chunks of 128 bytes along MN, each a box {128 B, BK rows}.
-template <int ELEM, int BK>
+template <int ELEM, int BK, bool MN_POSSIBLE>
 __device__ __forceinline__ void load_operand(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int mn, int row0,
                                              int rows, int kb) {
-  if (!mn) {
+  if (!MN_POSSIBLE || !mn) {
     tma_load_2d(dst, tm, bar, kb * BK, row0);
   } else {
     constexpr int CH = 128 / ELEM;  // elements per 128-byte chunk
     for (int c = 0; c * CH < rows; ++c) tma_load_2d(dst + c * (BK * 128), tm, bar, row0 + c * CH, kb * BK);
   }
 }
-template <int ELEM, int BK>
+template <int ELEM, int BK, bool MN_POSSIBLE>
 __device__ __forceinline__ void load_operand_pair(uint8_t* dst, const CUtensorMap* tm, uint32_t bar, int mn, int row0,
                                                   int rows, int kb) {
-  if (!mn) {
+  if (!MN_POSSIBLE || !mn) {
     tma_load_2d_pair(dst, tm, bar, kb * BK, row0);
   } else {
     constexpr int CH = 128 / ELEM;
     for (int c = 0; c * CH < rows; ++c) tma_load_2d_pair(dst + c * (BK * 128), tm, bar, row0 + c * CH, kb * BK);
   }
 }
-// Descriptor of the k-th UMMA_K slice of an operand tile, and what advancing k means per majorness.
+// Descriptors of an operand tile are `base + (smem address >> 4) + k * kstep` for the k-th UMMA_K slice: the
+// majorness only changes the constants, so the MMA-issuing thread (whose instruction count is on the critical
+// path) runs the same straight-line code for K-major and MN-major operands.
+struct OperandDesc {
+  uint64_t base;   // descriptor of a tile at shared-memory address 0
+  uint32_t kstep;  // K advance of one instruction, in 16-byte units
+};
 template <int BK, int UMMA_K>
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr, int mn, int k) {
-  if (!mn) return umma_desc_k_sw128(smem_addr) + 2 * k;                       // +32 bytes inside the swizzled row
-  return umma_desc_mn_sw128(smem_addr + k * (UMMA_K * 128), BK * 128);        // UMMA_K rows of 128 bytes further
+__device__ __forceinline__ OperandDesc make_operand_desc(int mn) {
+  OperandDesc d;
+  if (!mn) {
+    d.base = umma_desc_k_sw128(0);
+    d.kstep = 2;  // 32 bytes inside the swizzled row
+  } else {
+    d.base = umma_desc_mn_sw128(0, BK * 128);
+    d.kstep = (UMMA_K * 128) >> 4;  // UMMA_K rows of 128 bytes further
+  }
+  return d;
 }
 
 // Epilogue of one accumulator tile for one warp: its 32 TMEM lanes x BN columns go
 // TMEM -> registers -> (alpha, beta, convert) -> staging tile in shared memory -> TMA store.
 // After the last TMEM read the accumulator is handed back: an arrive on `acc_empty_local`, or,
 // when `acc_empty_remote` is non-zero, on that shared::cluster address (the pair leader's barrier).
-template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN>
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int NBUF = 2, bool RELEASE = true>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorMap* tmD, uint32_t t_addr, int m0,
                                               int n0, uint8_t* my_buf, int& nstore, int lane,
                                               uint64_t* acc_empty_local, uint32_t acc_empty_remote) {
@@ -104,11 +119,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
   // columns handled per TMA store: a 128-byte row for N-major output, 32 for M-major
   constexpr int SC = OUT_M_MAJOR ? 32 : (128 / (int)sizeof(OutT));
   constexpr int SUB = SC / 32;
-  const uint64_t store_policy = l2_policy_evict_first();
 #pragma unroll 1
   for (int c = 0; c < BN / SC; ++c) {
-    uint8_t* sb = my_buf + (nstore & 1) * EPI_BUF;
-    if (lane == 0) tma_store_wait_read<1>();  // the store that last used `sb` has drained
+    uint8_t* sb = my_buf + (nstore % NBUF) * EPI_BUF;
+    if (lane == 0) tma_store_wait_read<NBUF - 1>();  // the store that last used `sb` has drained
     __syncwarp();
 #pragma unroll
     for (int s = 0; s < SUB; ++s) {
@@ -116,7 +130,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
       const int col0 = c * SC + s * 32;
       tmem_ld_x32(t_addr + col0, v);
       tmem_ld_wait();
-      if (c == BN / SC - 1 && s == SUB - 1) {
+      if (RELEASE && c == BN / SC - 1 && s == SUB - 1) {
         // last read of this accumulator: hand it back to the MMA warp
         tc_fence_before_sync();
         __syncwarp();
@@ -184,12 +198,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      // D is written once and not read again by this kernel: mark it evict-first so that it does not
-      // push the A panel the tile group is re-using out of L2
       if constexpr (OUT_M_MAJOR)
-        tma_store_2d_hint(tmD, sb, m0, n0 + c * SC, store_policy);
+        tma_store_2d(tmD, sb, m0, n0 + c * SC);
       else
-        tma_store_2d_hint(tmD, sb, n0 + c * SC, m0, store_policy);
+        tma_store_2d(tmD, sb, n0 + c * SC, m0);
       tma_store_commit();
     }
     ++nstore;
@@ -252,49 +264,61 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mi, ni;
-        tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_PROD_EMPTY)) { ok = false; break; }
-          mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-          uint8_t* sa = smem + stage * STAGE_BYTES;
-          load_operand<ELEM, BK>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb);
-          load_operand<ELEM, BK>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      // the K-major-only loop is compiled separately: the producer's issue rate is on the critical path
+      auto produce = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+          int mi, ni;
+          tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_PROD_EMPTY)) { ok = false; break; }
+            mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb);
+            load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
         }
-      }
+      };
+      if (g.a_mn | g.b_mn) produce(std::true_type{});
+      else produce(std::false_type{});
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int lt = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
-        const int buf = lt & 1;
-        const uint32_t aphase = (lt >> 1) & 1;
-        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE_MMA_ACC)) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
-          if (!mbar_wait(&full[stage], phase, g.status, SITE_MMA_FULL)) { ok = false; break; }
+      auto issue = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;  // false: K-major constants fold at compile time
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int lt = 0;
+        const OperandDesc da = make_operand_desc<BK, UMMA_K>(MN ? g.a_mn : 0), db = make_operand_desc<BK, UMMA_K>(MN ? g.b_mn : 0);
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+          const int buf = lt & 1;
+          const uint32_t aphase = (lt >> 1) & 1;
+          if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE_MMA_ACC)) break;
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            tc_mma_ss<KIND>(d_tmem, operand_desc<BK, UMMA_K>(sa, g.a_mn, k),
-                            operand_desc<BK, UMMA_K>(sa + A_BYTES, g.b_mn, k), g.idesc, (kb | k) != 0 ? 1u : 0u);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&full[stage], phase, g.status, SITE_MMA_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint64_t ad = da.base + (sa >> 4), bd = db.base + ((sa + A_BYTES) >> 4);
+  #pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc_mma_ss<KIND>(d_tmem, ad + k * da.kstep, bd + k * db.kstep, g.idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          tc_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (ok) tc_commit(&acc_full[buf]);
         }
-        if (ok) tc_commit(&acc_full[buf]);
-      }
+      };
+      if (g.a_mn | g.b_mn) issue(std::true_type{});
+      else issue(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -407,64 +431,77 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        int mi, ni;
-        tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
-        const int row_a = mi * 256 + (int)rank * BM;
-        const int row_b = ni * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE2_PROD_EMPTY)) { ok = false; break; }
-          uint8_t* sa = smem + stage * STAGE_BYTES;
-          if (rank == 0) {
-            mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-            load_operand<ELEM, BK>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
-            load_operand<ELEM, BK>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, BN / 2, kb);
-          } else {
-            const uint32_t leader_full = mapa_shared(smem_u32(&full[stage]), 0);
-            mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);
-            load_operand_pair<ELEM, BK>(sa, &tmA, leader_full, g.a_mn, row_a, BM, kb);
-            load_operand_pair<ELEM, BK>(sa + A_BYTES, &tmB, leader_full, g.b_mn, row_b, BN / 2, kb);
+      // the K-major-only loop is compiled separately: the producer's issue rate is on the critical path
+      auto produce = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t leader_full0 = mapa_shared(smem_u32(&full[0]), 0);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+          int mi, ni;
+          tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+          const int row_a = mi * 256 + (int)rank * BM;
+          const int row_b = ni * BN + (int)rank * (BN / 2);
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE2_PROD_EMPTY)) { ok = false; break; }
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            if (rank == 0) {
+              mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
+              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, BN / 2, kb);
+            } else {
+              const uint32_t leader_full = leader_full0 + stage * 8;
+              mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);
+              load_operand_pair<ELEM, BK, MN>(sa, &tmA, leader_full, g.a_mn, row_a, BM, kb);
+              load_operand_pair<ELEM, BK, MN>(sa + A_BYTES, &tmB, leader_full, g.b_mn, row_b, BN / 2, kb);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-      }
+      };
+      if (g.a_mn | g.b_mn) produce(std::true_type{});
+      else produce(std::false_type{});
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int lt = 0;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++lt) {
-        const int buf = lt & 1;
-        const uint32_t aphase = (lt >> 1) & 1;
-        if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE2_MMA_ACC)) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < g.k_blocks; ++kb) {
-          if (!mbar_wait(&full[stage], phase, g.status, SITE2_MMA_FULL)) { ok = false; break; }
+      auto issue = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;  // false: K-major constants fold at compile time
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int lt = 0;
+        const OperandDesc da = make_operand_desc<BK, UMMA_K>(MN ? g.a_mn : 0), db = make_operand_desc<BK, UMMA_K>(MN ? g.b_mn : 0);
+        const uint32_t empty_local = smem_u32(&empty[0]), empty_peer = mapa_shared(empty_local, 1);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++lt) {
+          const int buf = lt & 1;
+          const uint32_t aphase = (lt >> 1) & 1;
+          if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE2_MMA_ACC)) break;
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            tc_mma_ss2<KIND>(d_tmem, operand_desc<BK, UMMA_K>(sa, g.a_mn, k),
-                             operand_desc<BK, UMMA_K>(sa + A_BYTES, g.b_mn, k), g.idesc, (kb | k) != 0 ? 1u : 0u);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&full[stage], phase, g.status, SITE2_MMA_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint64_t ad = da.base + (sa >> 4), bd = db.base + ((sa + A_BYTES) >> 4);
+  #pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc_mma_ss2<KIND>(d_tmem, ad + k * da.kstep, bd + k * db.kstep, g.idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit2(empty_local + stage * 8);  // frees this stage in the leader ...
+            tc_commit2(empty_peer + stage * 8);   // ... and in the peer
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          const uint32_t e_local = smem_u32(&empty[stage]);
-          tc_commit2(e_local);                  // frees this stage in the leader ...
-          tc_commit2(mapa_shared(e_local, 1));  // ... and in the peer
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (ok) {
+            const uint32_t f_local = smem_u32(&acc_full[buf]);
+            tc_commit2(f_local);
+            tc_commit2(mapa_shared(f_local, 1));
+          }
         }
-        if (ok) {
-          const uint32_t f_local = smem_u32(&acc_full[buf]);
-          tc_commit2(f_local);
-          tc_commit2(mapa_shared(f_local, 1));
-        }
-      }
+      };
+      if (g.a_mn | g.b_mn) issue(std::true_type{});
+      else issue(std::false_type{});
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
@@ -495,6 +532,188 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   tc_fence_before_sync();
   __syncthreads();
   // neither CTA may leave while its partner can still signal its barriers or read its operands
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------
+// CTA pairs on 256 x 512 tiles.  The pair kernel above is limited by how fast operands reach the
+// SMs (32 KB per SM and K block at 64 B/clk when the tensor pipe is busy, against a measured
+// L2 -> SM ceiling of about 68 B/clk/SM).  Doubling the tile along N lets two 256-wide MMAs share
+// every A stage: 48 KB per SM feed 1024 MMA cycles (47 B/clk).  The price is tensor memory: the
+// 128 x 512 fp32 accumulator of a CTA is all 512 columns, so it cannot be double-buffered.  The
+// two 256-column halves are drained by two epilogue warpgroups at the same time and handed back
+// separately, so the next tile's first half starts while the second is still draining.
+// Column j of half h belongs to global column n0 + (j / 128) * 256 + h * 128 + j % 128: that way
+// each CTA's share of B for both halves is ONE contiguous 256-row box.
+enum : int { SITEW_PROD_EMPTY = 121, SITEW_MMA_ACC = 122, SITEW_MMA_FULL = 123, SITEW_EPI_ACC = 124 };
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int STAGES>
+__global__ void __launch_bounds__(320, 1)
+gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                              const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+  constexpr int BM = 128;
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int BK = 128 / ELEM;
+  constexpr int UMMA_K = 32 / ELEM;
+  constexpr int A_BYTES = BM * 128;
+  constexpr int B_BYTES = 256 * 128;  // this CTA's 256 rows of the 512-row B tile
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int EPI_BUF = 4096;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + 8 * EPI_BUF);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;       // [1]
+  uint64_t* acc_empty = bars + 2 * STAGES + 1;  // [2], one per half
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 3);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int num_tiles = g.m_tiles * g.n_tiles;
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_empty[0], 8);
+    mbar_init(&acc_empty[1], 8);
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_holder, TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the K-major-only loop is compiled separately: the producer's issue rate is on the critical path
+      auto produce = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t leader_full0 = mapa_shared(smem_u32(&full[0]), 0);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+          int mi, ni;
+          tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+          const int row_a = mi * 256 + (int)rank * BM;
+          const int row_b = ni * 512 + (int)rank * 256;
+          for (int kb = 0; kb < g.k_blocks; ++kb) {
+            if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITEW_PROD_EMPTY)) { ok = false; break; }
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            if (rank == 0) {
+              mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
+              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, 256, kb);
+            } else {
+              const uint32_t leader_full = leader_full0 + stage * 8;
+              mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);
+              load_operand_pair<ELEM, BK, MN>(sa, &tmA, leader_full, g.a_mn, row_a, BM, kb);
+              load_operand_pair<ELEM, BK, MN>(sa + A_BYTES, &tmB, leader_full, g.b_mn, row_b, 256, kb);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      };
+      if (g.a_mn | g.b_mn) produce(std::true_type{});
+      else produce(std::false_type{});
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      auto issue = [&](auto mn_tag) {
+        constexpr bool MN = decltype(mn_tag)::value;  // false: K-major constants fold at compile time
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int lt = 0;
+        const OperandDesc da = make_operand_desc<BK, UMMA_K>(MN ? g.a_mn : 0), db = make_operand_desc<BK, UMMA_K>(MN ? g.b_mn : 0);
+        const uint32_t empty_local = smem_u32(&empty[0]), empty_peer = mapa_shared(empty_local, 1);
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++lt) {
+          const uint32_t aphase = lt & 1;
+          for (int kb = 0; kb < g.k_blocks && ok; ++kb) {
+            if (!mbar_wait(&full[stage], phase, g.status, SITEW_MMA_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+  #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (kb == 0) {  // this half of the accumulator must have been drained by both CTAs
+                if (!mbar_wait(&acc_empty[h], aphase ^ 1, g.status, SITEW_MMA_ACC)) { ok = false; break; }
+                tc_fence_after_sync();
+              }
+              const uint64_t ad = da.base + (sa >> 4), bd = db.base + ((sa + A_BYTES + h * (128 * 128)) >> 4);
+  #pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                tc_mma_ss2<KIND>(tmem_base + h * 256, ad + k * da.kstep, bd + k * db.kstep, g.idesc,
+                                 (kb | k) != 0 ? 1u : 0u);
+              }
+            }
+            if (!ok) break;
+            tc_commit2(empty_local + stage * 8);
+            tc_commit2(empty_peer + stage * 8);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (ok) {
+            const uint32_t f_local = smem_u32(&acc_full[0]);
+            tc_commit2(f_local);
+            tc_commit2(mapa_shared(f_local, 1));
+          }
+        }
+      };
+      if (g.a_mn | g.b_mn) issue(std::true_type{});
+      else issue(std::false_type{});
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue: warps 2..5 drain half 0, 6..9 half 1
+    const int q = warp & 3;
+    const int h = (warp - 2) >> 2;
+    uint8_t* my_buf = epi + (warp - 2) * EPI_BUF;
+    int nstore = 0;
+    int lt = 0;
+    for (int t = cluster_id; t < num_tiles; t += num_clusters, ++lt) {
+      int mi, ni;
+      tile_coord(t, g.m_tiles, g.n_tiles, g.group_m, mi, ni);
+      if (!mbar_wait(&acc_full[0], lt & 1, g.status, SITEW_EPI_ACC)) break;
+      tc_fence_after_sync();
+      const int m0 = mi * 256 + (int)rank * BM + q * 32;
+      const int n0 = ni * 512 + h * 128;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * 256;
+      const uint32_t remote = rank == 0 ? 0u : mapa_shared(smem_u32(&acc_empty[h]), 0);
+      epilogue_tile<KIND, OutT, OUT_M_MAJOR, 128, 1, false>(g, &tmD, t_addr, m0, n0, my_buf, nstore, lane, nullptr, 0u);
+      epilogue_tile<KIND, OutT, OUT_M_MAJOR, 128, 1, true>(g, &tmD, t_addr + 128, m0, n0 + 256, my_buf, nstore, lane,
+                                                           &acc_empty[h], remote);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  if (*reinterpret_cast<volatile int*>(g.status) != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
   cluster_arrive();
   cluster_wait();
   if (warp == 1) {
@@ -592,6 +811,40 @@ static int launch_pair_major(bool m_major, int bn, moye_b200_ctx* h, const CUten
                  : launch_pair_bn<KIND, OutT, false>(bn, h, ta, tb, td, args, stream);
 }
 
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR>
+static int launch_wide_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                            const GemmArgs& args, cudaStream_t stream) {
+  constexpr int STAGES = 4;
+  constexpr int SMEM = STAGES * (128 * 128 + 256 * 128) + 8 * 4096 + 256 + 1024;
+  auto kern = gemm_tcgen05_2cta_wide_kernel<KIND, OutT, OUT_M_MAJOR, STAGES>;
+  if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
+  const int tiles = args.m_tiles * args.n_tiles;
+  int clusters = h->num_sms / 2;
+  if (clusters > tiles) clusters = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(320, 1, 1);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MOYE_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, td, args));
+  return MOYE_OK;
+}
+
+template <int KIND, typename OutT>
+static int launch_wide_major(bool m_major, moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMap& tb,
+                             const CUtensorMap& td, const GemmArgs& args, cudaStream_t stream) {
+  return m_major ? launch_wide_inst<KIND, OutT, true>(h, ta, tb, td, args, stream)
+                 : launch_wide_inst<KIND, OutT, false>(h, ta, tb, td, args, stream);
+}
+
 int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                        const moye_gemm_params_t* p, cudaStream_t stream);
 
@@ -655,7 +908,20 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
 
   int bn = p.tile_n;
   if (bn == 0) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  const bool pair = p.path == 3 || (p.path == 0 && M > 128 && bn >= 128);
+  // path 4 = CTA pairs on 256 x 512 tiles.  Chosen automatically when it fills the SM pairs at least as well as
+  // 256 x 256 tiles do: it needs less operand traffic per flop and measured about 8 % faster on full waves.
+  bool wide = p.path == 4;
+  if (p.path == 0 && M > 128 && bn == 256 && N >= 512) {
+    const long long clusters = h->num_sms / 2;
+    auto fill = [&](long long tm, long long tn) {
+      const long long tiles = ((M + tm - 1) / tm) * ((N + tn - 1) / tn);
+      const long long waves = (tiles + clusters - 1) / clusters;
+      return (double)M * (double)N / ((double)waves * clusters * tm * tn);
+    };
+    wide = fill(256, 512) * 1.08 >= fill(256, 256);
+  }
+  if (wide) bn = 256;
+  const bool pair = wide || p.path == 3 || (p.path == 0 && M > 128 && bn >= 128);
   if (pair && bn < 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "CTA pairs take tile_n 128 or 256 (got %d)", bn);
 
   const int eb = dtype_bytes(A->dtype);
@@ -670,7 +936,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (b_mn) {
     if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, N, K, (uint64_t)B->stride[1] * eb, ch, bk, true)) return rc;
   } else {
-    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk, pair ? bn / 2 : bn, true))
+    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk,
+                              wide ? 256 : (pair ? bn / 2 : bn), true))
       return rc;
   }
   const int ob = dtype_bytes(out);
@@ -683,7 +950,7 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   GemmArgs a;
   a.M = (int)M; a.N = (int)N; a.K = (int)K;
   a.m_tiles = pair ? (int)((M + 255) / 256) : (int)((M + 127) / 128);
-  a.n_tiles = (int)((N + bn - 1) / bn);
+  a.n_tiles = wide ? (int)((N + 511) / 512) : (int)((N + bn - 1) / bn);
   a.k_blocks = (int)((K + bk - 1) / bk);
   // Tile groups: all column tiles of `group_m` row tiles run before the next group, so the group's A panel
   // (rows x K) is re-used from L2 while B streams through.  Size the panel at about 32 MB: the 126 MB L2 is two 63 MB halves, and a 67 MB panel measurably thrashes (DRAM reads 1.1 GB -> 1.3-1.4 GB at 8192^3).
@@ -705,6 +972,18 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   a.c_sn = (p.beta != 0.f) ? C->stride[1] : 0;
   a.status = h->d_status;
 
+  if (wide) {
+    if (kind == KIND_F16) {
+      if (out == MOYE_F32) return launch_wide_major<KIND_F16, float>(m_major, h, ta, tb, td, a, stream);
+      if (out == MOYE_F16) return launch_wide_major<KIND_F16, __half>(m_major, h, ta, tb, td, a, stream);
+      return launch_wide_major<KIND_F16, __nv_bfloat16>(m_major, h, ta, tb, td, a, stream);
+    } else if (kind == KIND_I8) {
+      return launch_wide_major<KIND_I8, int>(m_major, h, ta, tb, td, a, stream);
+    } else {
+      if (out == MOYE_F32) return launch_wide_major<KIND_F8, float>(m_major, h, ta, tb, td, a, stream);
+      return launch_wide_major<KIND_F8, __nv_bfloat16>(m_major, h, ta, tb, td, a, stream);
+    }
+  }
   if (pair) {
     if (kind == KIND_F16) {
       if (out == MOYE_F32) return launch_pair_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);

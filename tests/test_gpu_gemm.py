@@ -85,9 +85,9 @@ def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
     for m_major in (False, True):
         if m_major and (M * torch.empty(0, dtype=out_dtype).element_size()) % 16:
             continue
-        for path, tile_n in ((1, 0), (1, 64), (1, 128), (1, 256), (3, 128), (3, 256), (0, 0)):
+        for path, tile_n in ((1, 0), (1, 64), (1, 128), (1, 256), (3, 128), (3, 256), (4, 0), (0, 0)):
             C = out_tensor(M, N, out_dtype, dev, m_major)
-            mb.matmul(A, B, C, tile_n=tile_n, path=path)  # 1 = single CTAs, 3 = CTA pairs, 0 = library's choice
+            mb.matmul(A, B, C, tile_n=tile_n, path=path)  # 1 single CTAs, 3 CTA pairs, 4 pairs on 256x512 tiles, 0 auto
             mb.synchronize_status(dev)
             got = C.float().cpu().numpy() if kind != "s8" else C.cpu().numpy()
             if kind == "s8":
@@ -112,7 +112,7 @@ def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
         Ax = col_major(A) if a_mn else A
         Bx = col_major(B) if b_mn else B
         assert Ax.stride() == ((1, M) if a_mn else (K, 1))
-        for path in (1, 3):
+        for path in (1, 3, 4):
             for m_major in (False, True):
                 C = out_tensor(M, N, torch.float32, dev, m_major)
                 mb.matmul(Ax, Bx, C, path=path)
