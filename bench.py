@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM traffic of one launch of the 8192^3 fp16 GEMM kernel (dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu captures summarised under profiles/), bytes per launch.
-NCU_TRAFFIC_BYTES = {"gemm_f16_8192": 1.09e9 + 0.2515e9,       # profiles/gemm_tcgen05_2cta_f16_8192_dram_traffic.txt
+NCU_TRAFFIC_BYTES = {"gemm_f16_8192": 0.9137e9 + 0.2436e9,     # profiles/gemm_tcgen05_2cta_wide_f16_8192_dram_traffic.txt
                      "decode_bf16_16x28672x8192": 471.24e6 + 6.1e6,  # profiles/gemm_skinny_bf16_16x28672x8192.txt
                      "gemm_f16_4096x8192x4096": 179.6e6 + 100.5e6}
 
@@ -49,6 +49,10 @@ WORKLOADS = {
     # a smaller case of the same dense kernel (224 MB of operands + output, still larger than L2),
     # sized for multi-pass profiler captures
     "gemm_f16_4096x8192x4096": ("f16", 4096, 8192, 4096, "f32"),
+    # the same for the 256 x 512 tile kernel: 37 x 8 = 296 tiles = 4 full waves of the 74 SM pairs, 211 MB
+    "gemm_f16_9472x4096x2048": ("f16", 9472, 4096, 2048, "f32"),
+    # Float32 storage on the tf32 tensor-core kind, column-major like examples/gemm.jl (its literal element type)
+    "gemm_f32_8192_colmajor": ("f32", 8192, 8192, 8192, "f32"),
 }
 
 
@@ -125,6 +129,9 @@ def make_operands(torch, kind, M, N, K, out, dev, seed, colmajor=False):
     if kind == "f16":
         A = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).half()
         B = (torch.rand(N, K, device=dev, generator=g) * 2 - 1).half()
+    elif kind == "f32":
+        A = torch.rand(M, K, device=dev, generator=g) * 2 - 1
+        B = torch.rand(N, K, device=dev, generator=g) * 2 - 1
     elif kind == "bf16":
         A = (torch.randn(M, K, device=dev, generator=g) * 0.02).bfloat16()
         B = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
@@ -392,8 +399,8 @@ def extras(mb, torch, dev, peaks):
     """The other configurations, each timed alone for a few launches (reported beside the headline)."""
     out = {}
     stream = torch.cuda.current_stream()
-    for name in ("gemm_f16_4096", "gemm_f16_8192_colmajor", "gemm_bf16_8192", "gemm_s8_16384x8192x8192",
-                 "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192"):
+    for name in ("gemm_f16_4096", "gemm_f16_8192_colmajor", "gemm_bf16_8192", "gemm_f32_8192_colmajor",
+                 "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192"):
         kind, M, N, K, o = WORKLOADS[name]
         nset = 3 if M <= 32 else 1  # rotate weight buffers for the HBM-bound decode shape
         sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i, colmajor=name.endswith("_colmajor"))

@@ -131,9 +131,11 @@ int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
  * (src/algorithm/copy.jl:42-64), the `gemm!` tower (src/algorithm/blas.jl:11-131) and the
  * epilogue `copyto!(gC, rC)` (examples/gemm.jl:62), on tcgen05 tensor cores.
  * Supported (A,B -> accum -> D): f16,f16 -> f32 -> f32|f16; bf16,bf16 -> f32 -> f32|bf16;
- * s8,s8 -> s32 -> s32 (bit-exact); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b.
+ * s8,s8 -> s32 -> s32 (bit-exact); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b;
+ * f32,f32 -> f32 -> f32 on the tf32 tensor-core kind (operands are read with a 10-bit mantissa, the
+ * accumulation is fp32: the Float32 arrays of examples/gemm.jl run as they are, to about 1e-3 relative).
  * A and B may each be K-major (stride 1 along K) or, for f16 / bf16, MN-major (stride 1 along
- * M / N: MoYe's column-major arrays, the storage of examples/gemm.jl:92-93); 8-bit operands must be
+ * M / N: MoYe's column-major arrays, the storage of examples/gemm.jl:92-93; also f32); 8-bit operands must be
  * K-major.  D may be M-major or N-major.  The strided mode's pitch must be a multiple of 16 bytes.
  * C may be NULL when beta == 0.  Violations are errors, never fallbacks. */
 int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t* A,

@@ -113,7 +113,7 @@ def copyto_(*args, stream=None):
     return dst
 
 
-_AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.E4M3: "E4M3"}
+_AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.E4M3: "E4M3", _lib.F32: "TF32"}
 
 
 def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None):
@@ -156,7 +156,7 @@ def matmul(A, B, C, **kw):
     (a torch (rows, cols) tensor is taken with its own strides)."""
     A, B, C = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (A, B, C))
     if A.dtype not in _AB_TAG:
-        raise _lib.MoyeError(-2, "matmul takes f16, bf16, s8 or e4m3 operands on sm_100a")
+        raise _lib.MoyeError(-2, "matmul takes f16, bf16, f32 (as tf32), s8 or e4m3 operands on sm_100a")
     n = C.layout.shape[1]
     key = (A.dtype, 256 if n > 128 else (128 if n > 64 else 64))
     mma = _MMA_CACHE.get(key)

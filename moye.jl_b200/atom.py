@@ -13,6 +13,7 @@ New for sm_100a (what the hot path actually runs on):
   `MMAOP_SM100_128xNx16_F32F16F16F32_SS`, `..._F32BF16BF16F32_SS`  tcgen05.mma kind::f16
   `MMAOP_SM100_128xNx32_S32S8S8S32_SS`                             tcgen05.mma kind::i8
   `MMAOP_SM100_128xNx32_F32E4M3E4M3F32_SS`                         tcgen05.mma kind::f8f6f4
+  `MMAOP_SM100_128xNx8_F32TF32TF32F32_SS`                          tcgen05.mma kind::tf32 (Float32 storage)
   `CPOP_TMA_LOAD_SW128`, `CPOP_TMA_STORE`                          cp.async.bulk.tensor
 A tcgen05 instruction is issued by ONE thread for the whole CTA tile and accumulates in
 tensor memory, so its thread-id layout is `1:0` and its "fragments" are whole tiles.
@@ -33,7 +34,7 @@ __all__ = [
 DTYPE_BITS = {_lib.F32: 32, _lib.F16: 16, _lib.BF16: 16, _lib.S8: 8, _lib.U8: 8, _lib.E4M3: 8, _lib.S32: 32,
               _lib.U16: 16, _lib.U32: 32, _lib.U64: 64, _lib.U128: 128}
 _TAG = {"F32": _lib.F32, "F16": _lib.F16, "BF16": _lib.BF16, "S8": _lib.S8, "U8": _lib.U8, "S32": _lib.S32,
-        "E4M3": _lib.E4M3}
+        "E4M3": _lib.E4M3, "TF32": _lib.F32}
 
 
 def L(shape, stride=None):
@@ -106,13 +107,14 @@ _register_sm80()
 
 
 def sm100_mma_op(ab, n=256):
-    """The tcgen05 op for operand type `ab` ("F16", "BF16", "S8", "E4M3") and tile N.
+    """The tcgen05 op for operand type `ab` ("F16", "BF16", "S8", "E4M3", or "TF32" for Float32
+    storage read with a 10-bit mantissa) and tile N.
     One instruction covers 128 x n x K (K = 32 bytes of the operand type); one thread issues
     it and the accumulator lives in tensor memory, hence thr_id = 1:0 and value layouts that
     span the whole tile."""
     acc = "S32" if ab == "S8" else "F32"
-    k = 16 if ab in ("F16", "BF16") else 32
-    kind = {"F16": "kind::f16", "BF16": "kind::f16", "S8": "kind::i8", "E4M3": "kind::f8f6f4"}[ab]
+    k = 16 if ab in ("F16", "BF16") else (8 if ab == "TF32" else 32)
+    kind = {"F16": "kind::f16", "BF16": "kind::f16", "S8": "kind::i8", "E4M3": "kind::f8f6f4", "TF32": "kind::tf32"}[ab]
     name = f"MMAOP_SM100_128x{n}x{k}_{acc}{ab}{ab}{acc}_SS"
     if name not in MMA_OPS:
         MMA_OPS[name] = MMAOp(name, (128, n, k), _TAG[acc], _TAG[ab], _TAG[ab], _TAG[acc], L(1),
@@ -120,7 +122,7 @@ def sm100_mma_op(ab, n=256):
     return MMA_OPS[name]
 
 
-for _ab in ("F16", "BF16", "S8", "E4M3"):
+for _ab in ("F16", "BF16", "S8", "E4M3", "TF32"):
     for _n in (64, 128, 256):
         sm100_mma_op(_ab, _n)
 

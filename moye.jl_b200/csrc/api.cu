@@ -52,8 +52,8 @@ static bool tmap_dtype(int dt, CUtensorMapDataType* out) {
 }
 
 int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
-                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128) {
-  TmapKey key{ptr, dtype, dim0, dim1, stride1_bytes, box0, box1, swizzle128 ? 1 : 0};
+                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle) {
+  TmapKey key{ptr, dtype, dim0, dim1, stride1_bytes, box0, box1, swizzle};
   {
     std::lock_guard<std::mutex> lk(h->mu);
     auto it = h->tmaps.find(key);
@@ -74,14 +74,15 @@ int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype,
               (unsigned long long)stride1_bytes);
   if (box0 > 256 || box1 > 256 || ((uint64_t)box0 * eb) % 16 != 0)
     MOYE_FAIL(MOYE_ERR_INVALID_ARG, "bad TMA box %u x %u", box0, box1);
-  if (swizzle128 && (uint64_t)box0 * eb > 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "swizzled box wider than 128 bytes");
+  if (swizzle && (uint64_t)box0 * eb > 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "swizzled box wider than 128 bytes");
   cuuint64_t dims[2] = {dim0, dim1};
   cuuint64_t strides[1] = {dim1 > 1 ? stride1_bytes : (cuuint64_t)((dim0 * eb + 15) / 16 * 16)};
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  CUresult r = enc(&m, tdt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+  const CUtensorMapSwizzle sw = swizzle == TMAP_SWIZZLE_128B_ATOM_32B ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                : (swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+  CUresult r = enc(&m, tdt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     MOYE_FAIL(MOYE_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (dims %llu x %llu, pitch %llu, box %u x %u)",

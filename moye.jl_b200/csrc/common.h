@@ -85,9 +85,11 @@ namespace moye {
 //   dims  = {extent along the contiguous mode, extent along the strided mode}  (elements)
 //   stride1_bytes = byte stride of the strided mode (multiple of 16)
 //   box   = {box extent contiguous, box extent strided}
-//   swizzle128 = true selects CU_TENSOR_MAP_SWIZZLE_128B (box[0]*elem must be <= 128 bytes)
+//   swizzle = 0 none, 1 (or true) the 128-byte swizzle with 16-byte atoms, TMAP_SWIZZLE_128B_ATOM_32B the
+//   128-byte swizzle with 32-byte atoms (box[0]*elem must be <= 128 bytes when swizzled)
+enum { TMAP_SWIZZLE_NONE = 0, TMAP_SWIZZLE_128B = 1, TMAP_SWIZZLE_128B_ATOM_32B = 2 };
 int make_tmap_2d(moye_b200_ctx* h, CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
-                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);
+                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle);
 
 int encode_tmap_2d_uncached(CUtensorMap* out, const void* ptr, int dtype, uint64_t dim0, uint64_t dim1,
                             uint64_t stride1_bytes, uint32_t box0, uint32_t box1, bool swizzle128);

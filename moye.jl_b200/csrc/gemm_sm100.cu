@@ -100,7 +100,8 @@ __device__ __forceinline__ OperandDesc make_operand_desc(int mn) {
     d.base = umma_desc_k_sw128(0);
     d.kstep = 2;  // 32 bytes inside the swizzled row
   } else {
-    d.base = umma_desc_mn_sw128(0, BK * 128);
+    d.base = (BK == 32) ? umma_desc_mn_sw128_atom32(0, BK * 128)  // 32-bit elements (tf32): 32-byte swizzle atoms
+                        : umma_desc_mn_sw128(0, BK * 128);
     d.kstep = (UMMA_K * 128) >> 4;  // UMMA_K rows of 128 bytes further
   }
   return d;
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
   constexpr int BM = 128;
-  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : (KIND == KIND_TF32 ? 4 : 1);
   constexpr int BK = 128 / ELEM;       // one 128-byte swizzle row of K per stage
   constexpr int UMMA_K = 32 / ELEM;    // K of one tcgen05.mma
   constexpr int A_BYTES = BM * 128;
@@ -376,7 +377,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
   constexpr int BM = 128;              // rows per CTA; the pair covers 256
-  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : (KIND == KIND_TF32 ? 4 : 1);
   constexpr int BK = 128 / ELEM;
   constexpr int UMMA_K = 32 / ELEM;
   constexpr int A_BYTES = BM * 128;
@@ -558,7 +559,7 @@ __global__ void __launch_bounds__(320, 1)
 gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                               const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
   constexpr int BM = 128;
-  constexpr int ELEM = (KIND == KIND_F16) ? 2 : 1;
+  constexpr int ELEM = (KIND == KIND_F16) ? 2 : (KIND == KIND_TF32 ? 4 : 1);
   constexpr int BK = 128 / ELEM;
   constexpr int UMMA_K = 32 / ELEM;
   constexpr int A_BYTES = BM * 128;
@@ -870,19 +871,21 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     case MOYE_BF16: kind = KIND_F16; ab_fmt = 1; c_fmt = 1; break;
     case MOYE_S8: kind = KIND_I8; ab_fmt = 1; c_fmt = 2; break;
     case MOYE_E4M3: kind = KIND_F8; ab_fmt = 0; c_fmt = 1; break;
+    case MOYE_F32: kind = KIND_TF32; ab_fmt = 2; c_fmt = 1; break;  // operands are read as tf32 (10-bit mantissa)
     default: MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "operand dtype %d is not supported by the tcgen05 path", A->dtype);
   }
   const int out = D->dtype;
   const bool out_ok = (A->dtype == MOYE_F16 && (out == MOYE_F32 || out == MOYE_F16)) ||
                       (A->dtype == MOYE_BF16 && (out == MOYE_F32 || out == MOYE_BF16)) ||
                       (A->dtype == MOYE_S8 && out == MOYE_S32) ||
-                      (A->dtype == MOYE_E4M3 && (out == MOYE_BF16 || out == MOYE_F32));
+                      (A->dtype == MOYE_E4M3 && (out == MOYE_BF16 || out == MOYE_F32)) ||
+                      (A->dtype == MOYE_F32 && out == MOYE_F32);
   if (!out_ok) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
   // K-major (stride 1 along K) or MN-major (stride 1 along M / N, MoYe's column-major default)
   const bool a_mn = A->stride[1] != 1 || (K == 1 && A->stride[0] == 1 && M > 1);
   const bool b_mn = B->stride[1] != 1 || (K == 1 && B->stride[0] == 1 && N > 1);
-  if ((a_mn || b_mn) && kind != KIND_F16)
-    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "8-bit operands must be K-major (MN-major tiles are built for 16-bit types)");
+  if ((a_mn || b_mn) && kind != KIND_F16 && kind != KIND_TF32)
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "8-bit operands must be K-major (MN-major tiles are built for 16/32-bit types)");
   if ((a_mn && A->stride[0] != 1) || (b_mn && B->stride[0] != 1))
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B need a unit stride along K or along M / N; got A (%lld,%lld), B (%lld,%lld)",
               (long long)A->stride[0], (long long)A->stride[1], (long long)B->stride[0], (long long)B->stride[1]);
@@ -928,13 +931,15 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   const int bk = 128 / eb;
   CUtensorMap ta, tb, td;
   const int ch = 128 / eb;  // elements in one 128-byte chunk
+  // MN-major 32-bit tiles have one legal shared-memory form: the 128-byte swizzle with 32-byte atoms
+  const int mn_swizzle = eb == 4 ? TMAP_SWIZZLE_128B_ATOM_32B : TMAP_SWIZZLE_128B;
   if (a_mn) {
-    if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, M, K, (uint64_t)A->stride[1] * eb, ch, bk, true)) return rc;
+    if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, M, K, (uint64_t)A->stride[1] * eb, ch, bk, mn_swizzle)) return rc;
   } else {
     if (int rc = make_tmap_2d(h, &ta, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * eb, bk, 128, true)) return rc;
   }
   if (b_mn) {
-    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, N, K, (uint64_t)B->stride[1] * eb, ch, bk, true)) return rc;
+    if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, N, K, (uint64_t)B->stride[1] * eb, ch, bk, mn_swizzle)) return rc;
   } else {
     if (int rc = make_tmap_2d(h, &tb, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * eb, bk,
                               wide ? 256 : (pair ? bn / 2 : bn), true))
@@ -977,6 +982,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
       if (out == MOYE_F32) return launch_wide_major<KIND_F16, float>(m_major, h, ta, tb, td, a, stream);
       if (out == MOYE_F16) return launch_wide_major<KIND_F16, __half>(m_major, h, ta, tb, td, a, stream);
       return launch_wide_major<KIND_F16, __nv_bfloat16>(m_major, h, ta, tb, td, a, stream);
+    } else if (kind == KIND_TF32) {
+      return launch_wide_major<KIND_TF32, float>(m_major, h, ta, tb, td, a, stream);
     } else if (kind == KIND_I8) {
       return launch_wide_major<KIND_I8, int>(m_major, h, ta, tb, td, a, stream);
     } else {
@@ -989,6 +996,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
       if (out == MOYE_F32) return launch_pair_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);
       if (out == MOYE_F16) return launch_pair_major<KIND_F16, __half>(m_major, bn, h, ta, tb, td, a, stream);
       return launch_pair_major<KIND_F16, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+    } else if (kind == KIND_TF32) {
+      return launch_pair_major<KIND_TF32, float>(m_major, bn, h, ta, tb, td, a, stream);
     } else if (kind == KIND_I8) {
       return launch_pair_major<KIND_I8, int>(m_major, bn, h, ta, tb, td, a, stream);
     } else {
@@ -1000,6 +1009,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     if (out == MOYE_F32) return launch_major<KIND_F16, float>(m_major, bn, h, ta, tb, td, a, stream);
     if (out == MOYE_F16) return launch_major<KIND_F16, __half>(m_major, bn, h, ta, tb, td, a, stream);
     return launch_major<KIND_F16, __nv_bfloat16>(m_major, bn, h, ta, tb, td, a, stream);
+  } else if (kind == KIND_TF32) {
+    return launch_major<KIND_TF32, float>(m_major, bn, h, ta, tb, td, a, stream);
   } else if (kind == KIND_I8) {
     return launch_major<KIND_I8, int>(m_major, bn, h, ta, tb, td, a, stream);
   } else {

@@ -148,7 +148,7 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                : "memory");
 }
 
-enum MmaKind : int { KIND_F16 = 0, KIND_I8 = 1, KIND_F8 = 2 };
+enum MmaKind : int { KIND_F16 = 0, KIND_I8 = 1, KIND_F8 = 2, KIND_TF32 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; `accumulate` == 0 overwrites D.
 template <int KIND>
@@ -166,10 +166,16 @@ __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  } else if constexpr (KIND == KIND_F8) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
@@ -244,10 +250,16 @@ __device__ __forceinline__ void tc_mma_ss2(uint32_t d_tmem, uint64_t a_desc, uin
         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  } else if constexpr (KIND == KIND_F8) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
@@ -303,6 +315,19 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_byte_addr, 
   d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// The same for 32-bit elements (the tf32 kind), whose MN-major tiles exist in one shared-memory form only: the
+// 128-byte swizzle with 32-byte atoms (layout type 1).  A chunk is 32 elements (128 bytes) along MN, its K rows
+// are 128 bytes apart and 4 of them form one 512-byte swizzle atom (stride byte offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128_atom32(uint32_t smem_byte_addr, uint32_t chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_byte_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((chunk_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>(512 >> 4) << 32;                      // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(1) << 61;
   return d;
 }
 

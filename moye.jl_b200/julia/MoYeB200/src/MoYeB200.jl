@@ -46,6 +46,8 @@ struct MMAOP_SM100_128x256x16_F32F16F16F32_SS <: AbstractSM100MMAOP{Float32, Flo
 struct MMAOP_SM100_128x256x16_F32BF16BF16F32_SS <: AbstractSM100MMAOP{Float32, MoYe.BFloat16, MoYe.BFloat16, Float32} end
 struct MMAOP_SM100_128x256x32_S32S8S8S32_SS <: AbstractSM100MMAOP{Int32, Int8, Int8, Int32} end
 struct MMAOP_SM100_128x256x32_F32E4M3E4M3F32_SS <: AbstractSM100MMAOP{Float32, E4M3, E4M3, Float32} end
+# Float32 storage, read by the tensor core as tf32 (low 13 mantissa bits dropped), fp32 accumulation
+struct MMAOP_SM100_128x256x8_F32TF32TF32F32_SS <: AbstractSM100MMAOP{Float32, Float32, Float32, Float32} end
 struct CPOP_TMA_LOAD_SW128 <: AbstractCopyOp{Registers{UInt128, 1}, Registers{UInt128, 1}} end
 struct CPOP_TMA_STORE <: AbstractCopyOp{Registers{UInt128, 1}, Registers{UInt128, 1}} end
 # one thread issues a tcgen05 instruction for the whole CTA tile; the accumulator lives in tensor memory
@@ -54,6 +56,7 @@ MoYe.shape_mnk(::MMAOP_SM100_128x256x16_F32F16F16F32_SS) = MoYe.static((128, 256
 MoYe.shape_mnk(::MMAOP_SM100_128x256x16_F32BF16BF16F32_SS) = MoYe.static((128, 256, 16))
 MoYe.shape_mnk(::MMAOP_SM100_128x256x32_S32S8S8S32_SS) = MoYe.static((128, 256, 32))
 MoYe.shape_mnk(::MMAOP_SM100_128x256x32_F32E4M3E4M3F32_SS) = MoYe.static((128, 256, 32))
+MoYe.shape_mnk(::MMAOP_SM100_128x256x8_F32TF32TF32F32_SS) = MoYe.static((128, 256, 8))
 
 # ---- descriptor flattening: layout(x) -> (shape, stride) of a rank-2 view, 0-based element strides
 function moye_tensor(x::MoYeArray{T}) where {T}
@@ -107,6 +110,11 @@ end
 function matmul(A::CuMatrix{Float16}, B::CuMatrix{Float16}, C::CuMatrix{Float32})
     # K-major views of row-major storage: pass transposed CuArrays, e.g. A = CuArray(A_host')'
     mma = MoYe.make_tiled_mma(MMAOP_SM100_128x256x16_F32F16F16F32_SS())
+    MoYe.gemm!(mma, MoYeArray(C, size(C)), MoYeArray(A, size(A)), MoYeArray(B, size(B)))
+end
+# the literal examples/gemm.jl:91-96 call: column-major Float32 A (M,K), B (N,K), C (M,N)
+function matmul(A::CuMatrix{Float32}, B::CuMatrix{Float32}, C::CuMatrix{Float32})
+    mma = MoYe.make_tiled_mma(MMAOP_SM100_128x256x8_F32TF32TF32F32_SS())
     MoYe.gemm!(mma, MoYeArray(C, size(C)), MoYeArray(A, size(A)), MoYeArray(B, size(B)))
 end
 

@@ -193,6 +193,14 @@ def matmul_threads_f32(A, B, M, N, K, thread_layout=(4, 4), m_limit=0):
     return C
 
 
+def tf32_trunc(x):
+    """Float32 values as the tf32 tensor-core kind reads them: sign, 8 exponent bits and the top 10 mantissa
+    bits; the low 13 bits are dropped without rounding (measured on sm_100a: truncation reproduces the device
+    result to fp32 accumulation order, round-to-nearest does not)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
 def max_rel_err(got, ref):
     """max |got-ref| / max(|ref|, 1e-3 * max|ref|): the tolerance metric of every GEMM test."""
     got = np.asarray(got, dtype=np.float64)

@@ -11,7 +11,7 @@ import torch
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 NTHREADS = max(1, min(64, os.cpu_count() or 1))
-TOL = {"f16": 1e-2, "bf16": 1e-2, "e4m3": 3e-2}
+TOL = {"f16": 1e-2, "bf16": 1e-2, "e4m3": 3e-2, "f32": 1e-2}  # f32 runs on the tf32 kind (10-bit mantissa)
 
 
 def dev_bits(bits, dtype, shape, dev):
@@ -26,6 +26,11 @@ def operands(ho, kind, M, N, K, dev, seeds):
     if kind == "bf16":
         a, b = ho.normal_bf16_bits(seeds[0], (M * K,), 0.02), ho.normal_bf16_bits(seeds[1], (N * K,), 0.02)
         return a, b, dev_bits(a, torch.bfloat16, (M, K), dev), dev_bits(b, torch.bfloat16, (N, K), dev), ho.BF16
+    if kind == "f32":
+        # the device gets the raw Float32 values; the oracle gets them as the tf32 kind reads them (low 13 bits dropped)
+        a, b = ho.uniform_pm1(seeds[0], (M * K,)), ho.uniform_pm1(seeds[1], (N * K,))
+        return (ho.tf32_trunc(a), ho.tf32_trunc(b), torch.from_numpy(a).to(dev).view(M, K),
+                torch.from_numpy(b).to(dev).view(N, K), ho.F32)
     if kind == "s8":
         a, b = ho.uniform_s8(seeds[0], (M * K,)), ho.uniform_s8(seeds[1], (N * K,))
         return a, b, torch.from_numpy(a).to(dev).view(M, K), torch.from_numpy(b).to(dev).view(N, K), ho.S8
@@ -71,7 +76,7 @@ def test_small_goldens_all_dtypes(mb, ho, dev):
         assert ho.max_rel_err(Cb.float().cpu().numpy(), g["bf16_c"]) <= 1e-2
 
 
-@pytest.mark.parametrize("kind", ["f16", "bf16", "s8", "e4m3"])
+@pytest.mark.parametrize("kind", ["f16", "bf16", "s8", "e4m3", "f32"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 520, 1008), (1, 8, 16), (130, 72, 4096),
                                    (1024, 1024, 512)])
 def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
@@ -79,7 +84,8 @@ def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
     output majors."""
     a, b, A, B, dt = operands(ho, kind, M, N, K, dev, (3, 4))
     ref = ho.gemm_samples(a, b, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
-    out_dtype = {"f16": torch.float32, "bf16": torch.float32, "s8": torch.int32, "e4m3": torch.bfloat16}[kind]
+    out_dtype = {"f16": torch.float32, "bf16": torch.float32, "s8": torch.int32, "e4m3": torch.bfloat16,
+                 "f32": torch.float32}[kind]
     if kind == "e4m3" and N % 8:
         pytest.skip("bf16 rows of D must be 16-byte multiples")
     for m_major in (False, True):
@@ -101,7 +107,7 @@ def col_major(t):
     return t.t().contiguous().t()
 
 
-@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("kind", ["f16", "bf16", "f32"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 520, 1008), (136, 72, 4096), (2048, 1024, 512)])
 def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
     """A and / or B stored column-major, i.e. MN-major as in reference examples/gemm.jl:92-93
@@ -137,6 +143,26 @@ def test_examples_gemm_jl_storage(mb, ho, dev):
     want = np.stack([ho.gemm_f32(a32[r::M].copy(), (0, 1), b32, (1, N), 1, N, K, c_strides=(N, 1)) for r in rows])
     got = Cbuf.view(N, M).t()[torch.from_numpy(rows).to(dev)].cpu().numpy()
     assert ho.max_rel_err(got, want) <= 1e-2
+
+
+def test_examples_gemm_jl_float32(mb, ho, dev):
+    """The reference example with its own element type and sizes: Float32, 2048 x 2048 x 256, column-major
+    (reference examples/gemm.jl:91-96).  Float32 operands run on the tf32 tensor-core kind, which drops the low
+    13 mantissa bits of every operand: against the oracle on those truncated operands the result agrees like
+    every other float kind; against the fp32 host gemm! on the raw operands it is within 2^-9 sum|a||b| (2^-10 per operand)."""
+    M, N, K = 2048, 2048, 256
+    a, b = ho.rng(3).standard_normal(M * K, dtype=np.float32), ho.rng(4).standard_normal(N * K, dtype=np.float32)
+    A = mb.MoYeArray(torch.from_numpy(a).to(dev), mb.make_layout((M, K)))
+    B = mb.MoYeArray(torch.from_numpy(b).to(dev), mb.make_layout((N, K)))
+    Cbuf = torch.zeros(M * N, device=dev)
+    mb.matmul(A, B, mb.MoYeArray(Cbuf, mb.make_layout((M, N))))
+    mb.synchronize_status(dev)
+    got = Cbuf.cpu().numpy()
+    want = ho.gemm_f32(ho.tf32_trunc(a), (1, M), ho.tf32_trunc(b), (1, N), M, N, K)   # host gemm!, column-major, tf32 view
+    assert ho.max_rel_err(got, want) <= TOL["f32"]
+    raw = ho.gemm_f32(a, (1, M), b, (1, N), M, N, K)                                    # host gemm! on the raw Float32
+    bound = ho.gemm_f32(np.abs(a), (1, M), np.abs(b), (1, N), M, N, K)
+    assert np.all(np.abs(got - raw) <= 2.0 ** -9 * bound)
 
 
 def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
@@ -270,7 +296,8 @@ def test_gemm_argument_errors(mb, dev):
     assert call(B=T(buf.data_ptr(), F16, [128, 32], [32, 1])) == -4                   # K mismatch
     assert call(B=T(buf.data_ptr(), mb._lib.BF16, [128, 64], [64, 1])) == -2          # mixed operand types
     assert call(D=T(out.data_ptr(), mb._lib.S32, [128, 128], [128, 1])) == -2         # f16 -> s32 unsupported
-    assert call(A=T(buf.data_ptr(), F32, [128, 64], [64, 1]), B=T(buf.data_ptr(), F32, [128, 64], [64, 1])) == -2
+    assert call(A=T(buf.data_ptr(), F32, [128, 32], [32, 1]), B=T(buf.data_ptr(), F32, [128, 32], [32, 1])) == 0   # f32 -> tf32 kind
+    assert call(A=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1]), B=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1])) == -2
     assert call(p=mb._lib.GemmParams(1.0, 1.0, 1.0, 1.0, 0, 0, 0, 0)) == -1           # beta without C
     assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 96, 0, 0, 0)) == -1          # bad tile_n
     assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 2, 0)) == -4           # skinny path with M > 32
