@@ -367,7 +367,7 @@ def run_ours(args):
         "metric": metric, "value": value, "unit": munit, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": {"f16": "f16 (f32 accumulate)", "bf16": "bf16 (f32 accumulate)", "s8": "s8 (s32 accumulate)",
-                  "e4m3": "e4m3 (f32 accumulate)"}[kind],
+                  "e4m3": "e4m3 (f32 accumulate)", "f32": "f32 read as tf32 (f32 accumulate)"}[kind],
         "data": "synthetic", "config": workload_config(name, world), "clocks": clocks, "gpu_launches": args.steps,
         "e2e": {"value": e2e_val, "unit": munit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
