@@ -81,6 +81,21 @@ typedef struct {
   int64_t stride[MOYE_MAX_FLAT_RANK];
 } moye_layout_t;
 
+/* Fused epilogue, selected in moye_gemm_params_t.flags: one activation OR-ed with one bias mode.
+ * D = act(alpha*scale_a*scale_b*(A.B^T) + beta*C + bias), evaluated in fp32 before the output
+ * conversion.  The reference has no counterpart beyond `axpby!` (its README lists epilogue fusion
+ * as missing); the s8 -> s32 path and the skinny path (path 2) take neither. */
+enum {
+  MOYE_EPI_NONE = 0,
+  MOYE_EPI_RELU = 1,             /* max(x, 0) */
+  MOYE_EPI_GELU = 2,             /* x/2 * (1 + erf(x / sqrt 2)) */
+  MOYE_EPI_SILU = 3,             /* x / (1 + exp(-x)) */
+  MOYE_EPI_ACT_MASK = 0xF,
+  MOYE_EPI_BIAS_COL = 0x10,      /* bias[n], N floats: one value per column of D */
+  MOYE_EPI_BIAS_ROW = 0x20,      /* bias[m], M floats: one value per row of D */
+  MOYE_EPI_BIAS_MASK = 0x30
+};
+
 /* Parameters of the tiled GEMM.  alpha/beta follow `axpby!` (reference
  * src/algorithm/blas.jl:1-9): D = alpha*scale_a*scale_b*(A.B^T) + beta*C, and C is not read
  * when beta == 0.  Zero in a tiling field means "library default". */
@@ -94,7 +109,8 @@ typedef struct {
   int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel,
                                     3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
                                     4 CTA pairs on 256 x 512 tiles */
-  int32_t flags;                 /* reserved, must be 0 */
+  int32_t flags;                 /* fused epilogue: MOYE_EPI_* activation | MOYE_EPI_BIAS_*; 0 = plain GEMM */
+  const float* bias;             /* device pointer, fp32, read only when a bias mode is set */
 } moye_gemm_params_t;
 
 typedef enum {

@@ -44,7 +44,12 @@ class FlatLayout(ctypes.Structure):
 class GemmParams(ctypes.Structure):
     _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("scale_a", ctypes.c_float),
                 ("scale_b", ctypes.c_float), ("tile_n", ctypes.c_int32), ("split_k", ctypes.c_int32),
-                ("path", ctypes.c_int32), ("flags", ctypes.c_int32)]
+                ("path", ctypes.c_int32), ("flags", ctypes.c_int32), ("bias", ctypes.c_void_p)]
+
+
+# fused-epilogue selectors of GemmParams.flags (MOYE_EPI_* in the header)
+EPI_ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "silu": 3}
+EPI_BIAS_COL, EPI_BIAS_ROW = 0x10, 0x20
 
 
 class CopyParams(ctypes.Structure):

@@ -116,10 +116,39 @@ def copyto_(*args, stream=None):
 _AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.E4M3: "E4M3", _lib.F32: "TF32"}
 
 
-def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None):
+def _epilogue(bias, activation, D, dev):
+    """(flags, bias pointer, keep-alive) of the fused epilogue D = act(... + bias).  `bias` is a float32 CUDA
+    tensor with one value per column of D (length N) or per row (length M); when M == N pass `(tensor, "col")`
+    or `(tensor, "row")`."""
+    if activation not in _lib.EPI_ACT:
+        raise _lib.MoyeError(-1, f"unknown activation {activation!r}; one of relu, gelu, silu")
+    flags, ptr = _lib.EPI_ACT[activation], None
+    if bias is not None:
+        which = None
+        if isinstance(bias, tuple):
+            bias, which = bias
+        if not (torch.is_tensor(bias) and bias.is_cuda and bias.dtype == torch.float32 and bias.is_contiguous()
+                and bias.device == dev):
+            raise _lib.MoyeError(-1, "bias must be a contiguous float32 tensor on the device of D")
+        m, n = D.layout.shape[0], D.layout.shape[1]
+        if which is None:
+            if m == n and bias.numel() == n:
+                raise _lib.MoyeError(-1, "D is square: say (bias, 'col') or (bias, 'row')")
+            which = "col" if bias.numel() == n else ("row" if bias.numel() == m else None)
+        if which not in ("col", "row") or bias.numel() != (n if which == "col" else m):
+            raise _lib.MoyeError(-3, f"bias has {bias.numel()} values; D is {m} x {n}")
+        flags |= _lib.EPI_BIAS_COL if which == "col" else _lib.EPI_BIAS_ROW
+        ptr = bias.data_ptr()
+    return flags, ptr, bias
+
+
+def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None, bias=None,
+          activation=None):
     """`gemm!([tiled_mma,] D, A, B, C)`: D = alpha*scale_a*scale_b * A.B^T + beta*C with
     A:(M,K), B:(N,K), C and D:(M,N) in global memory.  `gemm_(A, B, C)` is `gemm!(C, A, B, C)`
-    like the reference's three-argument form (src/algorithm/blas.jl:11)."""
+    like the reference's three-argument form (src/algorithm/blas.jl:11).  `bias` (float32, one
+    value per column or per row of D) and `activation` ("relu", "gelu", "silu") are fused into the
+    epilogue: D = act(alpha*... + beta*C + bias), in fp32 before the output conversion."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
         tiled_mma, args = args[0], args[1:]
@@ -142,7 +171,8 @@ def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0
             tile_n = op.shape_mnk[1]  # one atom per CTA: the tile is the instruction's N
     lib, h = _lib.load(), _lib.handle(dev.index)
     st = stream if stream is not None else current_stream_ptr(dev)
-    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, 0)
+    flags, bias_ptr, _ = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if (C is not None and beta != 0.0) else None
     _lib.check(lib.moye_b200_gemm(h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB),
@@ -188,7 +218,7 @@ class LaunchPlan:
             _lib.check(rc)
 
 
-def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0):
+def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, bias=None, activation=None):
     """`gemm_` with the argument marshalling done once; returns a `LaunchPlan`."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
@@ -209,12 +239,13 @@ def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, pa
             raise _lib.MoyeError(-2, f"{op} cannot multiply these operands on sm_100a")
         tile_n = tile_n or op.shape_mnk[1]
     lib, h = _lib.load(), _lib.handle(dev.index)
-    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, 0)
+    flags, bias_ptr, bias = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if use_c else None
     argv = (h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB), ctypes.byref(tC) if use_c else None,
             ctypes.byref(p))
-    return LaunchPlan(lib.moye_b200_gemm, argv, dev, (D, A, B, C, p, tD, tA, tB, tC))
+    return LaunchPlan(lib.moye_b200_gemm, argv, dev, (D, A, B, C, p, tD, tA, tB, tC, bias))
 
 
 def plan_copy(*args):

@@ -32,7 +32,18 @@ struct GemmArgs {
   long long c_sm, c_sn;  // strides of C in elements
   int* status;
   int a_mn, b_mn;  // 1: the operand is MN-major (stride 1 along M / N) instead of K-major
+  const float* bias;  // fused epilogue: D = act(alpha*acc + beta*C + bias)
+  int bias_mode;      // 0 none, 1 one value per column n (length N), 2 one value per row m (length M)
+  int act;            // 0 none, 1 relu, 2 gelu (erf form), 3 silu
 };
+
+// The activations of the fused epilogue, on the fp32 value before the output conversion.
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == 1) return fmaxf(x, 0.f);
+  if (act == 2) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  if (act == 3) return x / (1.f + __expf(-x));
+  return x;
+}
 
 // Wait-site codes reported through the status word.
 enum : int { SITE_PROD_EMPTY = 101, SITE_MMA_ACC = 102, SITE_MMA_FULL = 103, SITE_EPI_ACC = 104 };
@@ -158,6 +169,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
       } else if constexpr (!INT_OUT) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha);
+      }
+      if constexpr (!INT_OUT) {
+        if (g.bias_mode | g.act) {  // uniform over the grid: the plain GEMM pays one predicated branch per chunk
+          const int row = m0 + lane;
+          const float brow = (g.bias_mode == 2 && row < g.M) ? __ldg(g.bias + row) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + col0 + j;
+            float x = __uint_as_float(v[j]) + brow;
+            if (g.bias_mode == 1 && col < g.N) x += __ldg(g.bias + col);
+            v[j] = __float_as_uint(apply_act(x, g.act));
+          }
+        }
       }
       if constexpr (OUT_M_MAJOR) {
         // staging tile is [32 columns][32 rows], rows contiguous: conflict-free
@@ -851,9 +875,14 @@ int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tens
 
 int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                 const moye_tensor_t* C, const moye_gemm_params_t* pp, cudaStream_t stream) {
-  moye_gemm_params_t p = {1.f, 0.f, 1.f, 1.f, 0, 0, 0, 0};
+  moye_gemm_params_t p = {1.f, 0.f, 1.f, 1.f, 0, 0, 0, 0, nullptr};
   if (pp) p = *pp;
-  if (p.flags != 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "flags must be 0");
+  const int act = p.flags & MOYE_EPI_ACT_MASK, bias_mode = (p.flags & MOYE_EPI_BIAS_MASK) >> 4;
+  if ((p.flags & ~(MOYE_EPI_ACT_MASK | MOYE_EPI_BIAS_MASK)) != 0 || act > MOYE_EPI_SILU || bias_mode > 2)
+    MOYE_FAIL(MOYE_ERR_INVALID_ARG, "unknown bits in flags (0x%x)", p.flags);
+  if (bias_mode != 0 && !p.bias) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "a bias mode is set but bias is NULL");
+  if (bias_mode != 0 && (reinterpret_cast<uintptr_t>(p.bias) & 3) != 0)
+    MOYE_FAIL(MOYE_ERR_MISALIGNED, "bias must be 4-byte aligned");
   if (A->rank != 2 || B->rank != 2 || D->rank != 2) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "A, B, D must be rank 2");
   const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
   if (B->shape[1] != K || D->shape[0] != M || D->shape[1] != N)
@@ -898,6 +927,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (kind == KIND_I8) {
     if (alpha != 1.f || (p.beta != 0.f && p.beta != 1.f))
       MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the s8 -> s32 path is exact integer arithmetic: alpha must be 1, beta 0 or 1");
+    if (act != 0 || bias_mode != 0)
+      MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the s8 -> s32 path takes no bias or activation (its epilogue is exact integer arithmetic)");
   }
   if (p.beta != 0.f) {
     if (!C || !C->ptr) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "beta != 0 needs C");
@@ -906,7 +937,10 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   }
 
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
-  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512 && !a_mn && !b_mn))
+  if (p.path == 2 && (act != 0 || bias_mode != 0))
+    MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the skinny path has no fused bias / activation; use path 0, 1, 3 or 4");
+  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512 && !a_mn && !b_mn &&
+                      act == 0 && bias_mode == 0))
     return launch_gemm_skinny(h, D, A, B, &p, stream);
 
   int bn = p.tile_n;
@@ -970,6 +1004,9 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
             ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
   a.a_mn = a_mn ? 1 : 0;
   a.b_mn = b_mn ? 1 : 0;
+  a.bias = bias_mode ? p.bias : nullptr;
+  a.bias_mode = bias_mode;
+  a.act = act;
   a.alpha = alpha;
   a.beta = p.beta;
   a.C = (p.beta != 0.f) ? C->ptr : nullptr;

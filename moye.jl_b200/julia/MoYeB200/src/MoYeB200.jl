@@ -22,7 +22,10 @@ end
 struct MoyeGemmParams
     alpha::Float32; beta::Float32; scale_a::Float32; scale_b::Float32
     tile_n::Int32; split_k::Int32; path::Int32; flags::Int32
+    bias::Ptr{Cvoid}   # Float32 device vector of the fused epilogue, C_NULL without one
 end
+const EPI_ACT = Dict(nothing => 0, :relu => 1, :gelu => 2, :silu => 3)   # MOYE_EPI_* of the header
+const EPI_BIAS_COL, EPI_BIAS_ROW = 0x10, 0x20
 struct MoyeCopyParams
     mode::Int32; tile_m::Int32; tile_n::Int32; flags::Int32
 end
@@ -83,9 +86,13 @@ check(rc) = rc == 0 ? nothing :
 # ---- gemm!(tiled_mma, D, A, B, C): replaces the whole matmul_kernel of examples/gemm.jl:4-64
 function MoYe.gemm!(mma::TiledMMA{<:MoYe.MMAAtom{<:MoYe.MMATraits{<:AbstractSM100MMAOP}}},
                     D::MoYeArray, A::MoYeArray, B::MoYeArray, C::Union{MoYeArray, Nothing} = nothing;
-                    alpha = 1, beta = 0, scale_a = 1f0, scale_b = 1f0, stream = CUDA.stream())
+                    alpha = 1, beta = 0, scale_a = 1f0, scale_b = 1f0, stream = CUDA.stream(),
+                    bias::Union{CuVector{Float32}, Nothing} = nothing, bias_along = :col, activation = nothing)
     all(MoYe.isgmem, (D, A, B)) || error("host-level gemm! needs global-memory arrays (no CPU fallback)")
-    p = Ref(MoyeGemmParams(alpha, beta, scale_a, scale_b, Int32(MoYe.tile_size(mma, MoYe._2)), 0, 0, 0))
+    # fused epilogue D = act(alpha*A*B' + beta*C + bias): bias[n] (:col) or bias[m] (:row)
+    flags = EPI_ACT[activation] | (bias === nothing ? 0 : (bias_along === :col ? EPI_BIAS_COL : EPI_BIAS_ROW))
+    bptr = bias === nothing ? C_NULL : Ptr{Cvoid}(UInt(pointer(bias)))
+    p = Ref(MoyeGemmParams(alpha, beta, scale_a, scale_b, Int32(MoYe.tile_size(mma, MoYe._2)), 0, 0, Int32(flags), bptr))
     tD, tA, tB = Ref(moye_tensor(D)), Ref(moye_tensor(A)), Ref(moye_tensor(B))
     tC = (C === nothing || iszero(beta)) ? C_NULL : Ref(moye_tensor(C))
     check(ccall((:moye_b200_gemm, libmoye_b200[]), Cint,

@@ -193,6 +193,29 @@ def matmul_threads_f32(A, B, M, N, K, thread_layout=(4, 4), m_limit=0):
     return C
 
 
+def fused_epilogue(acc, alpha=1.0, beta=0.0, C=None, bias=None, bias_mode=None, activation=None):
+    """D = act(alpha*acc + beta*C + bias) on an (M, N) float32 accumulator, in float64.  alpha / beta follow
+    the reference's `axpby!` (src/algorithm/blas.jl:1-9: the beta*C term is skipped when beta == 0); bias and
+    activation have no counterpart there and are defined here: bias_mode "col" adds bias[n], "row" adds bias[m];
+    relu = max(x, 0), gelu = x/2 (1 + erf(x / sqrt 2)), silu = x / (1 + exp(-x))."""
+    import math
+    x = np.asarray(acc, dtype=np.float64) * float(alpha)
+    if beta != 0.0:
+        x = x + float(beta) * np.asarray(C, dtype=np.float64)
+    if bias is not None:
+        b = np.asarray(bias, dtype=np.float64)
+        x = x + (b[None, :] if bias_mode == "col" else b[:, None])
+    if activation == "relu":
+        x = np.maximum(x, 0.0)
+    elif activation == "gelu":
+        x = 0.5 * x * (1.0 + np.frompyfunc(math.erf, 1, 1)(x / math.sqrt(2.0)).astype(np.float64))
+    elif activation == "silu":
+        x = x / (1.0 + np.exp(-x))
+    elif activation not in (None, "none"):
+        raise ValueError(activation)
+    return x.astype(np.float32)
+
+
 def tf32_trunc(x):
     """Float32 values as the tf32 tensor-core kind reads them: sign, 8 exponent bits and the top 10 mantissa
     bits; the low 13 bits are dropped without rounding (measured on sm_100a: truncation reproduces the device

@@ -47,7 +47,7 @@ def test_struct_layouts(mb):
     L = mb._lib
     assert ctypes.sizeof(L.Tensor) == 8 + 4 + 4 + 8 * 4 + 8 * 4
     assert ctypes.sizeof(L.FlatLayout) == 8 + 16 * L.MAX_FLAT_RANK
-    assert ctypes.sizeof(L.GemmParams) == 32 and ctypes.sizeof(L.CopyParams) == 16
+    assert ctypes.sizeof(L.GemmParams) == 40 and L.GemmParams.bias.offset == 32 and ctypes.sizeof(L.CopyParams) == 16
     assert L.Tensor.shape.offset == 16 and L.Tensor.stride.offset == 48
 
 

@@ -193,6 +193,62 @@ def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
     assert np.array_equal(C8.cpu().numpy(), ref8 + keep.cpu().numpy())
 
 
+@pytest.mark.parametrize("kind,out", [("f16", torch.float32), ("bf16", torch.bfloat16), ("e4m3", torch.bfloat16),
+                                      ("f32", torch.float32)])
+def test_fused_bias_activation_epilogue(mb, ho, dev, kind, out):
+    """D = act(alpha*A.B^T + beta*C + bias) in one launch, against the oracle's `fused_epilogue` on the oracle's
+    accumulator: both bias directions, the three activations, ragged edges, both output majors, every dense path."""
+    M, N, K = 384, 520, 1008
+    a, b, A, B, dt = operands(ho, kind, M, N, K, dev, (3, 4))
+    acc = ho.gemm_samples(a, b, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    sc = float(np.abs(acc).max())
+    bcol = ho.rng(31).standard_normal(N).astype(np.float32) * np.float32(0.5 * sc)
+    brow = ho.rng(32).standard_normal(M).astype(np.float32) * np.float32(0.5 * sc)
+    cin = (ho.rng(33).standard_normal((M, N)).astype(np.float32) * np.float32(0.3 * sc))
+    Bc, Br = torch.from_numpy(bcol).to(dev), torch.from_numpy(brow).to(dev)
+    tol = {torch.float32: TOL[kind], torch.bfloat16: max(TOL[kind], 1e-2)}[out]
+    cases = [(1, 256, False, "col", "relu", 0.0), (1, 64, True, "row", "gelu", 0.0), (3, 256, False, "row", "silu", 0.5),
+             (3, 128, True, "col", None, 0.0), (4, 0, False, "col", "gelu", 0.0), (4, 0, True, "row", "relu", 1.0),
+             (0, 0, False, None, "silu", 0.0), (0, 0, False, "col", None, 2.0)]
+    for path, tile_n, m_major, which, act, beta in cases:
+        if m_major and (M * torch.empty(0, dtype=out).element_size()) % 16:
+            continue
+        alpha = 1.0 / sc                                   # brings x to O(1), where the activations bend
+        bias = {None: None, "col": bcol * np.float32(alpha), "row": brow * np.float32(alpha)}[which]
+        Cin = torch.from_numpy(cin * np.float32(alpha)).to(dev).to(out)
+        if m_major:
+            Cin = Cin.t().contiguous().t()
+        D = out_tensor(M, N, out, dev, m_major)
+        tb = None if which is None else ((Bc if which == "col" else Br) * alpha).contiguous()
+        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(Cin) if beta else None, alpha=alpha,
+                 beta=beta, tile_n=tile_n, path=path, bias=tb, activation=act)
+        mb.synchronize_status(dev)
+        want = ho.fused_epilogue(acc, alpha, beta, Cin.float().cpu().numpy(), bias, which, act)
+        err = ho.max_rel_err(D.float().cpu().numpy(), want)
+        assert err <= tol, (path, tile_n, m_major, which, act, beta, err)
+
+
+def test_fused_epilogue_argument_errors(mb, ho, dev):
+    M, N, K = 128, 128, 64
+    a, b, A, B, _ = operands(ho, "f16", M, N, K, dev, (3, 4))
+    D = torch.zeros(M, N, device=dev)
+    bias = torch.zeros(N, device=dev)
+    with pytest.raises(mb.MoyeError):          # square D: the direction must be named
+        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, bias=bias)
+    with pytest.raises(mb.MoyeError):
+        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, bias=(torch.zeros(7, device=dev), "col"))
+    with pytest.raises(mb.MoyeError):
+        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, activation="tanh")
+    with pytest.raises(mb.MoyeError):          # the skinny path has no fused epilogue
+        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, activation="relu", path=2)
+    a8, b8, A8, B8, _ = operands(ho, "s8", M, N, K, dev, (5, 6))
+    with pytest.raises(mb.MoyeError):          # the integer path stays exact integer arithmetic
+        mb.gemm_(mb.MoYeArray(torch.zeros(M, N, device=dev, dtype=torch.int32)), mb.MoYeArray(A8), mb.MoYeArray(B8), None,
+                 activation="relu")
+    mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, bias=(bias, "row"), activation="relu")
+    mb.synchronize_status(dev)
+
+
 def sampled_check(mb, ho, dev, kind, M, N, K, seeds, out_dtype, tol, nsample=128, **kw):
     a, b, A, B, dt = operands(ho, kind, M, N, K, dev, seeds)
     C = torch.zeros(M, N, dtype=out_dtype, device=dev)
