@@ -44,6 +44,8 @@ WORKLOADS = {
     "gemm_e4m3_16384x8192x8192": ("e4m3", 16384, 8192, 8192, "bf16"),
     "decode_bf16_16x28672x8192": ("bf16", 16, 28672, 8192, "bf16"),
     "copy_f16_8192": ("copy", 8192, 8192, 0, "f16"),
+    # copyto!(dest, transpose(src)), the reference's transpose_kernel at the copy workload's size (fp16 and fp32)
+    "transpose_8192": ("transpose", 8192, 8192, 0, "f16"),
     # the storage of the reference's examples/gemm.jl: A (M,K), B (N,K), C (M,N) all column-major
     "gemm_f16_8192_colmajor": ("f16", 8192, 8192, 8192, "f32"),
     # a smaller case of the same dense kernel (224 MB of operands + output, still larger than L2),
@@ -194,7 +196,7 @@ def run_reference_arm(args):
     ho, _ = ge.load_oracle()
     ho.lib()
     kind, M, N, K, out = WORKLOADS[args.workload]
-    if kind == "copy":
+    if kind in ("copy", "transpose"):
         raise SystemExit("the reference arm times the GEMM workloads")
     threads = os.cpu_count() or 1
     total = args.steps + args.warmup
@@ -271,8 +273,8 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    if kind == "copy":
-        return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier)
+    if kind in ("copy", "transpose"):
+        return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier, transpose=kind == "transpose")
 
     A, B, C = make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank, colmajor=name.endswith("_colmajor"))
     kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
@@ -423,6 +425,7 @@ def extras(mb, torch, dev, peaks):
         del sets, plans
         torch.cuda.empty_cache()
     out["copy_f16_8192"] = copy_rates(mb, torch, dev, peaks, 20, 5)
+    out["transpose_8192"] = transpose_rates(mb, torch, dev, peaks, 20, 5)
     mb.synchronize_status(dev)
     return out
 
@@ -451,11 +454,38 @@ def copy_rates(mb, torch, dev, peaks, steps, warmup):
     return res
 
 
-def run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier):
+def transpose_rates(mb, torch, dev, peaks, steps, warmup):
+    """`copyto!(dest, transpose(src))` of an 8192 x 8192 matrix (the reference's transpose_kernel, test/host/copy_async.jl:51-95,
+    at the copy workload's size), rotating 4 buffer pairs so that the traffic is HBM's."""
+    m = n = 8192
+    res = {}
+    stream = torch.cuda.current_stream()
+    for label, dt in (("f16", torch.float16), ("f32", torch.float32)):
+        nset = 4 if dt == torch.float16 else 2  # each set exceeds the 126 MB L2 together with its destination
+        srcs = [(torch.rand(n * m, device=dev) * 2 - 1).to(dt) for _ in range(nset)]
+        dsts = [torch.zeros_like(s) for s in srcs]
+        plans = [mb.plan_copy(mb.MoYeArray(d, mb.make_layout((m, n))), mb.transpose(mb.MoYeArray(s, mb.make_layout((n, m)))))
+                 for d, s in zip(dsts, srcs)]
+        sp = mb.current_stream_ptr(dev)
+        i = [0]
+
+        def fn():
+            i[0] += 1
+            plans[i[0] % nset](sp)
+
+        ms = time_launches(torch, fn, steps, warmup, stream)
+        gbs = 2.0 * m * n * srcs[0].element_size() / ms / 1e6
+        res[label] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+        del srcs, dsts, plans
+        torch.cuda.empty_cache()
+    return res
+
+
+def run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier, transpose=False):
     sampler = ClockSampler(dev.index)
     barrier()
     sampler.start()
-    res = copy_rates(mb, torch, dev, peaks, args.steps, max(3, args.warmup))
+    res = (transpose_rates if transpose else copy_rates)(mb, torch, dev, peaks, args.steps, max(3, args.warmup))
     barrier()
     clocks = sampler.stop()
     best = max(res.values(), key=lambda r: r["GB/s"])
@@ -463,12 +493,13 @@ def run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier):
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    nbytes = 2.0 * 8192 * 8192 * 2
-    line = {"metric": "copy GB/s", "value": nbytes * world / ms / 1e6, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+    nbytes = best["GB/s"] * best["ms"] * 1e6
+    line = {"metric": "transposing copy GB/s" if transpose else "copy GB/s", "value": nbytes * world / ms / 1e6, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 (bytes)", "data": "synthetic",
-            "config": {"workload": "copy_f16_8192", "tile": "128x64", "atoms": "128-bit", "sharding": f"row blocks x{world}",
-                       "l2": "4 rotating buffer pairs, 134 MB each"},
+            "config": {"workload": "transpose_8192" if transpose else "copy_f16_8192",
+                       "tile": "TMA stages of 16 KB" if transpose else "128x64", "atoms": "128-bit",
+                       "sharding": f"row blocks x{world}", "l2": "rotating buffer pairs, 134 MB or more each"},
             "clocks": clocks, "gpu_launches": args.steps * len(res), "kernels": res,
             "roofline": {"bound": "hbm", "achieved": best["GB/s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": best["GB/s"] / peaks["hbm_gbs"], "traffic": None, "peak_source": f"hbm copy, of {peak_src}"}}

@@ -116,7 +116,11 @@ typedef struct {
 typedef enum {
   MOYE_COPY_AUTO = 0,
   MOYE_COPY_UNIVERSAL128 = 1,    /* 128-bit UniversalCopy atoms, gmem -> smem -> gmem */
-  MOYE_COPY_TMA = 2              /* cp.async.bulk.tensor load + store through an smem ring */
+  MOYE_COPY_TMA = 2,             /* cp.async.bulk.tensor load + store through an smem ring */
+  MOYE_COPY_TRANSPOSE = 3        /* src and dst contiguous along different modes: TMA load, 128-bit register
+                                    transposition between two swizzled smem tiles, TMA store (the automatic choice
+                                    for such operands; takes over `transpose_kernel`, reference
+                                    test/host/copy_async.jl:51-74) */
 } moye_copy_mode_t;
 
 typedef struct {
@@ -158,10 +162,12 @@ int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t*
                    const moye_tensor_t* B, const moye_tensor_t* C,
                    const moye_gemm_params_t* params, void* stream);
 
-/* dst = src for two rank-2 tensors of equal shape and dtype whose first mode is contiguous,
- * tile by tile through shared memory.  Takes over `copy_kernel` (reference
- * test/host/copy_async.jl:3-25) and `copyto!(tiled_copy, dst, src)` with 128-bit atoms
- * (src/algorithm/copy.jl:106-130, src/arch/copy/copy.jl:26-51). */
+/* dst = src for two rank-2 tensors of equal shape and dtype, each contiguous along one mode,
+ * tile by tile through shared memory.  Both contiguous along the same mode: takes over
+ * `copy_kernel` (reference test/host/copy_async.jl:3-25) and `copyto!(tiled_copy, dst, src)`
+ * with 128-bit atoms (src/algorithm/copy.jl:106-130, src/arch/copy/copy.jl:26-51).  Contiguous
+ * along different modes (`copyto!(dest, transpose(src))`; elements of 1, 2, 4 or 8 bytes): takes
+ * over `transpose_kernel` (test/host/copy_async.jl:51-74). */
 int moye_b200_copy(moye_handle_t h, const moye_tensor_t* dst, const moye_tensor_t* src,
                    const moye_copy_params_t* params, void* stream);
 

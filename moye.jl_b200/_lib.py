@@ -15,7 +15,7 @@ MAX_FLAT_RANK = 12
 F32, F16, BF16, S8, U8, E4M3, S32, U16, U32, U64, U128 = range(11)
 DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, U8: 1, E4M3: 1, S32: 4, U16: 2, U32: 4, U64: 8, U128: 16}
 
-COPY_AUTO, COPY_UNIVERSAL128, COPY_TMA = 0, 1, 2
+COPY_AUTO, COPY_UNIVERSAL128, COPY_TMA, COPY_TRANSPOSE = 0, 1, 2, 3
 
 STATUS_NAMES = {
     0: "OK", -1: "INVALID_ARG", -2: "UNSUPPORTED_DTYPE", -3: "UNSUPPORTED_LAYOUT", -4: "UNSUPPORTED_SHAPE",

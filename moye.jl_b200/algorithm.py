@@ -92,7 +92,11 @@ def copyto_(*args, stream=None):
         params = _lib.CopyParams(mode, tm, tn, 0)
     sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
     tiled_ok = (sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0] and sd_d[1][0] == 1 and sd_s[1][0] == 1)
-    if tiled_ok:
+    # one unit stride each, in different modes (`copyto!(dest, transpose(src))`) or both in the second mode: the
+    # library picks the transposing kernel or swaps the modes; explicit tiled copies keep the reference's contract
+    other_ok = (tiled_copy is None and not tiled_ok and sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0]
+                and 1 in sd_d[1] and 1 in sd_s[1])
+    if tiled_ok or other_ok:
         td = _lib.make_tensor(dst.ptr, dst.dtype, sd_d[0], sd_d[1])
         ts = _lib.make_tensor(src.ptr, src.dtype, sd_s[0], sd_s[1])
         rc = lib.moye_b200_copy(h, ctypes.byref(td), ctypes.byref(ts), ctypes.byref(params) if params else None, st)
@@ -249,15 +253,19 @@ def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, pa
 
 
 def plan_copy(*args):
-    """`copyto_([tiled_copy,] dst, src)` for the tiled (rank-2, contiguous first mode) case, prepared once."""
+    """`copyto_([tiled_copy,] dst, src)` for the tiled (rank-2, contiguous first mode) case, prepared once.
+    Without a TiledCopy the operands may be contiguous along different modes (the transposing copy)."""
     if len(args) == 3:
         tiled_copy, dst, src = args
     else:
         (dst, src), tiled_copy = args, None
     dev = _need_gmem(dst, src)
     sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
-    if sd_d is None or sd_s is None or sd_d[0] != sd_s[0] or sd_d[1][0] != 1 or sd_s[1][0] != 1:
-        raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode")
+    same_first = sd_d is not None and sd_s is not None and sd_d[1][0] == 1 and sd_s[1][0] == 1
+    one_unit_each = tiled_copy is None and sd_d is not None and sd_s is not None and 1 in sd_d[1] and 1 in sd_s[1]
+    if sd_d is None or sd_s is None or sd_d[0] != sd_s[0] or not (same_first or one_unit_each):
+        raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode "
+                                 "(without a TiledCopy: each contiguous along one mode)")
     if dst.storage.dtype != src.storage.dtype:
         raise _lib.MoyeError(-2, "copyto!: element types differ")
     params = None

@@ -14,7 +14,7 @@ from .layout import (COLON, Layout, _c2i0, _off, _tup, _unwrap1, dice_tuple, get
                      zipped_divide)
 
 __all__ = ["MoYeArray", "isgmem", "local_tile", "local_partition", "tile", "parallelize", "zeros_",
-           "make_fragment_like_array", "recast", "TORCH_TO_MOYE"]
+           "make_fragment_like_array", "recast", "transpose", "TORCH_TO_MOYE"]
 
 TORCH_TO_MOYE = {
     torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.int8: _lib.S8,
@@ -165,6 +165,16 @@ def make_fragment_like_array(x, dtype=None):
     l = _fragment_layout(x.layout)
     buf = torch.empty(size(l), dtype=dtype or x.storage.dtype, device=x.device)
     return MoYeArray(buf, l)
+
+
+def transpose(x):
+    """`MoYe.transpose(x)`: the same memory seen with its two modes swapped; of a rank-2 `Layout`, the layout
+    `make_layout(l[2], l[1])` (reference src/array.jl:247-249, src/layout.jl:772-774)."""
+    if isinstance(x, Layout):
+        if len(x) != 2:
+            raise ValueError("transpose takes a rank-2 layout")
+        return make_layout(x[1], x[0])
+    return MoYeArray(x, transpose(x.layout))
 
 
 def recast(x, new_dtype):

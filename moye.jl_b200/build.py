@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "lib", "libmoye_b200.so")
-SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_skinny.cu", "copy_sm100.cu", "layout_sm100.cu"]
+SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_skinny.cu", "copy_sm100.cu", "transpose_sm100.cu", "layout_sm100.cu"]
 HEADERS = ["common.h", "ptx.cuh", os.path.join("..", "..", "include", "moye_b200.h")]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-shared"]

@@ -115,6 +115,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
                 const moye_tensor_t* C, const moye_gemm_params_t* p, cudaStream_t stream);
 int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t* src, const moye_copy_params_t* p,
                 cudaStream_t stream);
+int launch_transpose(moye_b200_ctx* h, void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int dtype,
+                     int64_t m, int64_t n, cudaStream_t stream);
 int launch_layout_copy(moye_b200_ctx* h, void* dst, const moye_layout_t* dl, const void* src,
                        const moye_layout_t* sl, int elem_bytes, cudaStream_t stream);
 int launch_layout_eval(moye_b200_ctx* h, const moye_layout_t* l, int64_t first, int64_t n, int64_t* out,

@@ -16,6 +16,8 @@
 //      straight out of the same tile; loads run LOOKAHEAD tiles ahead of stores (6 slots, 2 ahead,
 //      two CTAs per SM).
 // Both are HBM-bound: algorithmic traffic is one read plus one write of the tensor.
+#include <utility>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -149,12 +151,22 @@ static int ilog2_exact(long long v) {
   return (1ll << l) == v ? l : -1;
 }
 
-int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t* src, const moye_copy_params_t* pp,
+int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst_in, const moye_tensor_t* src_in, const moye_copy_params_t* pp,
                 cudaStream_t stream) {
   moye_copy_params_t p = {MOYE_COPY_AUTO, 0, 0, 0};
   if (pp) p = *pp;
   if (p.flags != 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "flags must be 0");
-  if (dst->rank != 2 || src->rank != 2) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "tiled copy takes rank-2 tensors");
+  if (dst_in->rank != 2 || src_in->rank != 2) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "tiled copy takes rank-2 tensors");
+  moye_tensor_t dst_v = *dst_in, src_v = *src_in;
+  if (src_v.stride[1] == 1 && dst_v.stride[1] == 1 && !(src_v.stride[0] == 1 && dst_v.stride[0] == 1)) {
+    // both row-major: the same copy with the modes of both views (and of the tile) swapped
+    for (moye_tensor_t* t : {&dst_v, &src_v}) {
+      std::swap(t->shape[0], t->shape[1]);
+      std::swap(t->stride[0], t->stride[1]);
+    }
+    std::swap(p.tile_m, p.tile_n);
+  }
+  const moye_tensor_t *dst = &dst_v, *src = &src_v;
   if (dst->dtype != src->dtype) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "dst and src dtypes differ");
   const int eb = dtype_bytes(src->dtype);
   if (eb == 0) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "unknown dtype %d", src->dtype);
@@ -163,6 +175,18 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t*
   if (m == 0 || n == 0) return MOYE_OK;  // nothing to move
   if (m < 0 || n < 0) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "negative extent");
   if (!dst->ptr || !src->ptr) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "null data pointer");
+  // operands of different majorness: the transposing kernel (`copyto!(dest, transpose(src))`)
+  const bool s0 = src->stride[0] == 1 || m == 1, s1 = src->stride[1] == 1 || n == 1;
+  const bool d0 = dst->stride[0] == 1 || m == 1, d1 = dst->stride[1] == 1 || n == 1;
+  if (p.mode == MOYE_COPY_TRANSPOSE || (p.mode == MOYE_COPY_AUTO && !(s0 && d0) && ((s1 && d0) || (s0 && d1)))) {
+    if (p.tile_m != 0 || p.tile_n != 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the transposing copy chooses its own tiles");
+    if (src->stride[1] == 1 && dst->stride[0] == 1)
+      return launch_transpose(h, dst->ptr, dst->stride[1], src->ptr, src->stride[0], src->dtype, m, n, stream);
+    if (src->stride[0] == 1 && dst->stride[1] == 1)  // the mirrored case: swap the modes of both views
+      return launch_transpose(h, dst->ptr, dst->stride[0], src->ptr, src->stride[1], src->dtype, n, m, stream);
+    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT,
+              "the transposing copy needs src with stride 1 along one mode and dst with stride 1 along the other");
+  }
   if (src->stride[0] != 1 || dst->stride[0] != 1)
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "tiled copy needs stride 1 along the first mode of both tensors");
   if (m > INT32_MAX / 4 || n > INT32_MAX / 4) MOYE_FAIL(MOYE_ERR_TOO_LARGE, "extent too large");

@@ -135,6 +135,73 @@ def test_tiled_copy_matches_reference_copy_kernel(mb, ho, dev):
         mb.copyto_(narrow, mb.MoYeArray(dst, mb.make_layout((m, n))), mb.MoYeArray(src, mb.make_layout((m, n))))
 
 
+def _rand(dtype, numel, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.rand(numel, generator=g) * 2 - 1).to(dtype)
+    return torch.randint(-120, 120, (numel,), generator=g).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float16, torch.float32, torch.int64])
+@pytest.mark.parametrize("m,n", [(2048, 2048), (1008, 528), (16, 16), (16, 4096), (4096, 16), (8192, 3008)])
+def test_transposing_copy_bit_exact(mb, ho, dev, dtype, m, n):
+    """`copyto!(dest, transpose(src))` (reference test/host/copy_async.jl:51-74 and :77-95): operands contiguous
+    along different modes go through the transposing kernel; bytes must match the oracle's copy through the two
+    layouts (checked in full on the small shapes) and torch's transpose."""
+    b = _rand(dtype, n * m, 11).to(dev)                  # b: (n, m) column-major, like the reference's `b`
+    a = torch.zeros(m * n, dtype=dtype, device=dev)      # a: (m, n) column-major
+    A = mb.MoYeArray(a, mb.make_layout((m, n)))
+    B = mb.MoYeArray(b, mb.make_layout((n, m)))
+    mb.copyto_(A, mb.transpose(B))                       # a == transpose(b)
+    mb.synchronize_status(dev)
+    assert torch.equal(a.view(n, m), b.view(m, n).t())   # torch views are row-major: a[j][i] = A(i, j)
+    if m * n <= 1 << 20:
+        want = np.zeros(m * n, dtype=a.cpu().numpy().dtype)
+        ho.copy_layout(want, (m, n), (1, m), b.cpu().numpy(), (m, n), (n, 1))
+        assert np.array_equal(a.cpu().numpy(), want)
+    # the mirrored pair: source column-major, destination row-major
+    c = torch.zeros(m * n, dtype=dtype, device=dev)
+    mb.copyto_(mb.MoYeArray(c, mb.make_layout((m, n), (n, 1))), A)
+    mb.synchronize_status(dev)
+    assert torch.equal(c.view(m, n), a.view(n, m).t())
+    # both row-major: the plain tiled copy with the modes swapped
+    d = torch.zeros(m * n, dtype=dtype, device=dev)
+    mb.copyto_(mb.MoYeArray(d, mb.make_layout((m, n), (n, 1))), mb.MoYeArray(c, mb.make_layout((m, n), (n, 1))))
+    mb.synchronize_status(dev)
+    assert torch.equal(d, c)
+
+
+def test_transposing_copy_pitched_views_leave_padding_alone(mb, dev):
+    m, n, lds, ldd = 1000, 264, 272, 1008              # src rows of 272 elements hold 264; dst columns of 1008 hold 1000
+    src = _rand(torch.float32, m * lds, 12).to(dev)
+    dst = torch.full((n * ldd,), 7.0, dtype=torch.float32, device=dev)
+    S = mb.MoYeArray(src, mb.make_layout((m, n), (lds, 1)))
+    D = mb.MoYeArray(dst, mb.make_layout((m, n), (1, ldd)))
+    mb.copyto_(D, S)
+    mb.synchronize_status(dev)
+    d = dst.view(n, ldd)
+    assert torch.equal(d[:, :m], src.view(m, lds)[:, :n].t())
+    assert bool((d[:, m:] == 7).all()), "the copy wrote outside the destination view"
+
+
+def test_transposing_copy_errors(mb, dev):
+    lib, h = mb._lib.load(), mb._lib.handle(dev.index)
+    st = mb.current_stream_ptr(dev)
+    buf = torch.zeros(1 << 16, dtype=torch.float16, device=dev)
+    T = lambda off, shape, stride: mb._lib.make_tensor(buf.data_ptr() + off, mb._lib.F16, shape, stride)
+    p = mb._lib.CopyParams(mb._lib.COPY_TRANSPOSE, 0, 0, 0)
+    same = lib.moye_b200_copy(h, ctypes.byref(T(0, [64, 64], [1, 64])), ctypes.byref(T(32768, [64, 64], [1, 64])),
+                              ctypes.byref(p), st)
+    assert same == -3                                   # both contiguous along the same mode: not a transpose
+    odd = lib.moye_b200_copy(h, ctypes.byref(T(0, [64, 60], [1, 64])), ctypes.byref(T(32768, [64, 60], [60, 1])),
+                             None, st)
+    assert odd == -5                                    # 120-byte source rows
+    tiled = mb._lib.CopyParams(mb._lib.COPY_TRANSPOSE, 32, 32, 0)
+    assert lib.moye_b200_copy(h, ctypes.byref(T(0, [64, 64], [1, 64])), ctypes.byref(T(32768, [64, 64], [64, 1])),
+                              ctypes.byref(tiled), st) == -1
+    mb.synchronize_status(dev)
+
+
 def test_empty_and_invalid_copies(mb, dev):
     lib, h = mb._lib.load(), mb._lib.handle(dev.index)
     st = mb.current_stream_ptr(dev)
@@ -147,7 +214,7 @@ def test_empty_and_invalid_copies(mb, dev):
     a, b = T(buf.data_ptr(), [64, 8], [1, 64]), T(buf.data_ptr() + 4096, [64, 8], [1, 64])
     cases = [
         (T(buf.data_ptr() + 2, [64, 8], [1, 64]), a, -5),            # misaligned base
-        (T(buf.data_ptr(), [64, 8], [8, 1]), a, -3),                # not contiguous along mode 1
+        (T(buf.data_ptr(), [64, 8], [2, 128]), a, -3),              # no unit stride
         (T(buf.data_ptr(), [64, 4], [1, 64]), a, -4),               # shape mismatch
         (T(buf.data_ptr(), [64, 8], [1, 64], mb._lib.BF16), a, -2),  # dtype mismatch
         (T(buf.data_ptr(), [60, 8], [1, 60]), T(buf.data_ptr() + 4096, [60, 8], [1, 60]), -5),  # 120-byte columns
