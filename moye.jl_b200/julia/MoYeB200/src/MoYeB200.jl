@@ -113,6 +113,16 @@ function Base.copyto!(tc::TiledCopy, dst::MoYeArray{T, 2, ViewEngine{T, CuPtr{T}
     return dst
 end
 
+# ---- copyto!(dst, src) on global-memory arrays, each contiguous along one mode.  `copyto!(a, MoYe.transpose(b))`
+# replaces transpose_kernel of test/host/copy_async.jl:51-95 (the library picks the transposing kernel).
+function Base.copyto!(dst::MoYeArray{T, 2, ViewEngine{T, CuPtr{T}}}, src::MoYeArray{T, 2, ViewEngine{T, CuPtr{T}}};
+                      stream = CUDA.stream()) where {T}
+    check(ccall((:moye_b200_copy, libmoye_b200[]), Cint,
+                (Ptr{Cvoid}, Ref{MoyeTensor}, Ref{MoyeTensor}, Ptr{Cvoid}, Ptr{Cvoid}),
+                handle(), Ref(moye_tensor(dst)), Ref(moye_tensor(src)), C_NULL, stream.handle))
+    return dst
+end
+
 # ---- matmul(A, B, C) of examples/gemm.jl:66-89, on the tcgen05 atom for eltype(A)
 function matmul(A::CuMatrix{Float16}, B::CuMatrix{Float16}, C::CuMatrix{Float32})
     # K-major views of row-major storage: pass transposed CuArrays, e.g. A = CuArray(A_host')'
