@@ -104,7 +104,8 @@ typedef struct {
   float beta;
   float scale_a;                 /* per-tensor dequantisation scales (fp8 path); 1 otherwise */
   float scale_b;
-  int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128 */
+  int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128.  Widened to 128 (256 on
+                                    CTA pairs) when B is MN-major with 8-bit elements */
   int32_t split_k;               /* skinny path only: 0 = auto */
   int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel,
                                     3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
@@ -154,9 +155,9 @@ int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
  * s8,s8 -> s32 -> s32 (bit-exact); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b;
  * f32,f32 -> f32 -> f32 on the tf32 tensor-core kind (operands are read with a 10-bit mantissa, the
  * accumulation is fp32: the Float32 arrays of examples/gemm.jl run as they are, to about 1e-3 relative).
- * A and B may each be K-major (stride 1 along K) or, for f16 / bf16, MN-major (stride 1 along
- * M / N: MoYe's column-major arrays, the storage of examples/gemm.jl:92-93; also f32); 8-bit operands must be
- * K-major.  D may be M-major or N-major.  The strided mode's pitch must be a multiple of 16 bytes.
+ * A and B may each be K-major (stride 1 along K) or MN-major (stride 1 along M / N: MoYe's
+ * column-major arrays, the storage of examples/gemm.jl:92-93), for every operand type.
+ * D may be M-major or N-major.  The strided mode's pitch must be a multiple of 16 bytes.
  * C may be NULL when beta == 0.  Violations are errors, never fallbacks. */
 int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t* A,
                    const moye_tensor_t* B, const moye_tensor_t* C,

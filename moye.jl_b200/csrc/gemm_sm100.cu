@@ -913,8 +913,6 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   // K-major (stride 1 along K) or MN-major (stride 1 along M / N, MoYe's column-major default)
   const bool a_mn = A->stride[1] != 1 || (K == 1 && A->stride[0] == 1 && M > 1);
   const bool b_mn = B->stride[1] != 1 || (K == 1 && B->stride[0] == 1 && N > 1);
-  if ((a_mn || b_mn) && kind != KIND_F16 && kind != KIND_TF32)
-    MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "8-bit operands must be K-major (MN-major tiles are built for 16/32-bit types)");
   if ((a_mn && A->stride[0] != 1) || (b_mn && B->stride[0] != 1))
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "A and B need a unit stride along K or along M / N; got A (%lld,%lld), B (%lld,%lld)",
               (long long)A->stride[0], (long long)A->stride[1], (long long)B->stride[0], (long long)B->stride[1]);
@@ -960,8 +958,14 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (wide) bn = 256;
   const bool pair = wide || p.path == 3 || (p.path == 0 && M > 128 && bn >= 128);
   if (pair && bn < 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "CTA pairs take tile_n 128 or 256 (got %d)", bn);
-
   const int eb = dtype_bytes(A->dtype);
+  if (b_mn && eb == 1) {
+    // an MN-major tile is loaded in chunks of 128 bytes along N = 128 8-bit elements: a CTA's share of B must be
+    // at least that wide (single CTAs: tile_n >= 128; pairs: tile_n 256, i.e. 128 columns per CTA); a narrower
+    // request is widened
+    const int need = pair ? 256 : 128;
+    if (bn < need) bn = need;
+  }
   const int bk = 128 / eb;
   CUtensorMap ta, tb, td;
   const int ch = 128 / eb;  // elements in one 128-byte chunk

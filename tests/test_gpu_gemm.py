@@ -107,8 +107,8 @@ def col_major(t):
     return t.t().contiguous().t()
 
 
-@pytest.mark.parametrize("kind", ["f16", "bf16", "f32"])
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 520, 1008), (136, 72, 4096), (2048, 1024, 512)])
+@pytest.mark.parametrize("kind", ["f16", "bf16", "f32", "s8", "e4m3"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 528, 1008), (144, 80, 4096), (2048, 1024, 512)])
 def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
     """A and / or B stored column-major, i.e. MN-major as in reference examples/gemm.jl:92-93
     (A = randn(M, K), B = randn(N, K) in Julia), on both dense kernels."""
@@ -120,10 +120,13 @@ def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
         assert Ax.stride() == ((1, M) if a_mn else (K, 1))
         for path in (1, 3, 4):
             for m_major in (False, True):
-                C = out_tensor(M, N, torch.float32, dev, m_major)
+                C = out_tensor(M, N, torch.int32 if kind == "s8" else torch.float32, dev, m_major)
                 mb.matmul(Ax, Bx, C, path=path)
                 mb.synchronize_status(dev)
-                assert ho.max_rel_err(C.cpu().numpy(), ref) <= TOL[kind], (a_mn, b_mn, path, m_major)
+                if kind == "s8":
+                    assert np.array_equal(C.cpu().numpy(), ref), (a_mn, b_mn, path, m_major)
+                else:
+                    assert ho.max_rel_err(C.cpu().numpy(), ref) <= TOL[kind], (a_mn, b_mn, path, m_major)
 
 
 def test_examples_gemm_jl_storage(mb, ho, dev):
@@ -362,7 +365,8 @@ def test_gemm_argument_errors(mb, dev):
     A8 = T(buf.data_ptr(), mb._lib.S8, [128, 64], [64, 1])
     D32 = T(out.data_ptr(), mb._lib.S32, [128, 128], [128, 1])
     assert call(D=D32, A=A8, B=A8, p=mb._lib.GemmParams(2.0, 0.0, 1.0, 1.0, 0, 0, 0, 0)) == -1  # s8 path is exact
-    assert call(D=D32, A=T(buf.data_ptr(), mb._lib.S8, [128, 64], [1, 128]), B=A8) == -3   # 8-bit operands: K-major only
+    assert call(D=D32, A=T(buf.data_ptr(), mb._lib.S8, [128, 64], [1, 128]), B=A8) == 0    # 8-bit operands may be MN-major
+    assert call(D=D32, A=T(buf.data_ptr(), mb._lib.S8, [128, 64], [2, 256]), B=A8) == -3   # but need one unit stride
     mb.synchronize_status(dev)
 
 
