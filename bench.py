@@ -380,6 +380,25 @@ def run_ours(args):
                      "kernel": "gemm_tcgen05_2cta_wide_kernel" if not bytes_bound else "gemm_skinny_kernel",
                      "kernel_ms": ms},
     }
+    if dist is not None and world > 1 and not args.no_extras and not bytes_bound:
+        # outside the timed path: reassembling the M-sharded C on every rank over NCCL, reported on its own
+        try:
+            mb.all_gather_rows(C, M * world, world)
+            barrier()
+            e0.record(stream)
+            for _ in range(3):
+                full = mb.all_gather_rows(C, M * world, world)
+            e1.record(stream)
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            shard_bytes = C.numel() * C.element_size()
+            line["allgather_c"] = {"ms": float(t.item()), "shard_bytes": shard_bytes,
+                                   "busbw_GB/s": shard_bytes * (world - 1) / float(t.item()) / 1e6,
+                                   "how": "torch.distributed all_gather (NCCL) of the row shards + concatenation, not in `value`"}
+            del full
+        except Exception as exc:  # reported, never hidden
+            line["allgather_c"] = {"error": repr(exc)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ho, _ = ge.load_oracle()
         threads = os.cpu_count() or 1
