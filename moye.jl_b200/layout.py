@@ -20,7 +20,7 @@ __all__ = [
     "composition", "complement", "right_inverse", "left_inverse", "logical_product", "zipped_product",
     "tiled_product", "blocked_product", "raked_product", "tile_to_shape", "logical_divide", "zipped_divide",
     "tiled_divide", "upcast", "downcast", "recast_layout", "make_fragment_like", "max_common_vector",
-    "get_congr_coord", "append_layout", "prepend_layout", "group_modes", "Swizzle",
+    "get_congr_coord", "append_layout", "prepend_layout", "group_modes", "Swizzle", "print_layout",
 ]
 
 COLON = ":"
@@ -693,3 +693,21 @@ class Swizzle:
 
     def __repr__(self):
         return f"Swizzle({self.bits},{self.base},{self.shift})"
+
+
+def print_layout(layout, file=None):
+    """`print_layout(layout)` for a rank-2 layout: the table of 1-based indices, rows = mode 1, columns = mode 2
+    (reference src/print.jl:7-44, same cell widths and rulers).  Returns the text as well."""
+    if len(layout) != 2:
+        raise ValueError("print_layout takes a rank-2 layout")
+    rows, cols = size(layout[0]), size(layout[1])
+    w = len(str(cosize(layout))) + 2
+    rule = "    " + ("+-----------------"[:w + 1]) * cols + "+"
+    out = [repr(layout), "    " + "".join("  " + str(n).rjust(w - 2) + " " for n in range(1, cols + 1))]
+    for m in range(1, rows + 1):
+        out.append(rule)
+        out.append(str(m).rjust(2) + "  " + "".join("| " + str(layout(m, n)).rjust(w - 2) + " " for n in range(1, cols + 1)) + "|")
+    out.append(rule)
+    text = "\n".join(out)
+    print(text, file=file)
+    return text

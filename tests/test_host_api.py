@@ -281,3 +281,21 @@ def test_host_operands_are_rejected(mb):
         mb.gemm_(c, a, a, None)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         mb.copyto_(a, a)
+
+
+def test_print_layout_table(mb):
+    """Same table as the reference's print_layout (src/print.jl:7-44): header, rulers of ndigits(cosize)+3
+    characters per cell, 1-based indices right-aligned."""
+    import io
+    buf = io.StringIO()
+    text = mb.print_layout(mb.make_layout((2, 3), (3, 1)), file=buf)
+    want = "\n".join(["(2, 3):(3, 1)",
+                      "      1   2   3 ",
+                      "    +---+---+---+",
+                      " 1  | 1 | 2 | 3 |",
+                      "    +---+---+---+",
+                      " 2  | 4 | 5 | 6 |",
+                      "    +---+---+---+"])
+    assert text == want and buf.getvalue() == want + "\n"
+    wide = mb.print_layout(mb.make_layout(((2, 2), 4), ((1, 8), 2)), file=io.StringIO()).splitlines()
+    assert wide[2] == "    +----+----+----+----+" and wide[3] == " 1  |  1 |  3 |  5 |  7 |"
