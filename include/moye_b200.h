@@ -84,7 +84,7 @@ typedef struct {
 /* Fused epilogue, selected in moye_gemm_params_t.flags: one activation OR-ed with one bias mode.
  * D = act(alpha*scale_a*scale_b*(A.B^T) + beta*C + bias), evaluated in fp32 before the output
  * conversion.  The reference has no counterpart beyond `axpby!` (its README lists epilogue fusion
- * as missing); the s8 -> s32 path and the skinny path (path 2) take neither. */
+ * as missing); the s8 -> s32 path takes neither. */
 enum {
   MOYE_EPI_NONE = 0,
   MOYE_EPI_RELU = 1,             /* max(x, 0) */
@@ -107,7 +107,7 @@ typedef struct {
   int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128.  Widened to 128 (256 on
                                     CTA pairs) when B is MN-major with 8-bit elements */
   int32_t split_k;               /* skinny path only: 0 = auto */
-  int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel,
+  int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel (M <= 128),
                                     3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
                                     4 CTA pairs on 256 x 512 tiles */
   int32_t flags;                 /* fused epilogue: MOYE_EPI_* activation | MOYE_EPI_BIAS_*; 0 = plain GEMM */

@@ -187,17 +187,19 @@ def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0
 def matmul(A, B, C, **kw):
     """`matmul(A, B, C)` of reference examples/gemm.jl:66-89: C = A * B' for device arrays,
     with the tcgen05 atom chosen from the operand type.  Accepts MoYeArrays or torch tensors
-    (a torch (rows, cols) tensor is taken with its own strides)."""
+    (a torch (rows, cols) tensor is taken with its own strides).  Without `tile_n` the library
+    picks the tile width and the kernel from the problem shape; with `tile_n` (64, 128, 256) the
+    product runs on the atom of that width."""
     A, B, C = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (A, B, C))
     if A.dtype not in _AB_TAG:
         raise _lib.MoyeError(-2, "matmul takes f16, bf16, f32 (as tf32), s8 or e4m3 operands on sm_100a")
-    n = C.layout.shape[1]
-    key = (A.dtype, 256 if n > 128 else (128 if n > 64 else 64))
+    tile_n = kw.pop("tile_n", 0)
+    if tile_n == 0:
+        return gemm_(C, A, B, None, **kw)
+    key = (A.dtype, tile_n)
     mma = _MMA_CACHE.get(key)
     if mma is None:
         mma = _MMA_CACHE[key] = make_tiled_mma(sm100_mma_op(_AB_TAG[key[0]], key[1]))
-    if "tile_n" in kw and kw["tile_n"] == 0:
-        kw.pop("tile_n")
     return gemm_(mma, C, A, B, None, **kw)
 
 

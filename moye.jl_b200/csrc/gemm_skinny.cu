@@ -1,4 +1,4 @@
-// Skinny (decode-shaped) GEMM for sm_100a: D(M,N) = alpha * X(M,K) . W(N,K)^T with M <= 32.
+// Skinny (decode-shaped) GEMM for sm_100a: D(M,N) = alpha * X(M,K) . W(N,K)^T with M <= 128.
 //
 // The product is bound by reading W once from HBM, so the kernel is organised around keeping
 // as many W bytes in flight as possible:
@@ -29,6 +29,9 @@ struct SkinnyArgs {
   float alpha;
   void* D;
   long long d_sm, d_sn;  // element strides of D
+  const float* bias;     // fused epilogue D = act(alpha * acc + bias); see moye_gemm_params_t.flags
+  int bias_mode;         // 0 none, 1 bias[n], 2 bias[m]
+  int act;               // 0 none, 1 relu, 2 gelu, 3 silu
   int* tickets;          // [n_tiles], zero between launches
   float* partials;       // [grid][2][NX][128] fp32
   int* status;
@@ -180,41 +183,65 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const uint32_t aphase = (seg >> 1) & 1;
       if (!epi_all(mbar_wait(&acc_full[buf], aphase, g.status, SITE_SK_EPI))) break;
       tc_fence_after_sync();
-      float acc[NX];
-      {
-        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NX;
-        if constexpr (NX == 16) {
+      // The accumulator is drained in chunks of CH columns (= rows of X) so that NX up to 128 needs no more
+      // registers than NX = 32; the accumulator buffer is handed back after the last chunk has been read.
+      constexpr int CH = NX < 32 ? NX : 32;
+      const int n_local = q * 32 + lane;
+      const int n = tile * 128 + n_local;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NX;
+      auto load_chunk = [&](int c0, float (&acc)[CH]) {
+        if constexpr (CH == 16) {
           uint32_t v[16];
-          tmem_ld_x16(t_addr, v);
+          tmem_ld_x16(t_addr + c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(v[j]);
         } else {
           uint32_t v[32];
-          tmem_ld_x32(t_addr, v);
+          tmem_ld_x32(t_addr + c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
         }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
-
-      const int n_local = q * 32 + lane;
-      const int n = tile * 128 + n_local;
+        if (c0 + CH == NX) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+      };
+      // D(m, n) = act(alpha * x + bias): bias per output column n (one value per thread) or per row m
+      const float bias_n = (g.bias_mode == 1 && n < g.N) ? __ldg(g.bias + n) : 0.f;
+      auto finish = [&](int m, float x) {
+        float v = x * g.alpha + bias_n;
+        if (g.bias_mode == 2) v += __ldg(g.bias + m);
+        if (g.act == 1) v = fmaxf(v, 0.f);
+        else if (g.act == 2) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+        else if (g.act == 3) v = v / (1.f + __expf(-v));
+        store_out<OutT>(g.D, (long long)m * g.d_sm + (long long)n * g.d_sn, v);
+      };
       if (whole) {
-        if (n < g.N) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < NX; c0 += CH) {
+          float acc[CH];
+          load_chunk(c0, acc);
+          if (n < g.N) {
 #pragma unroll
-          for (int m = 0; m < NX; ++m)
-            if (m < g.M) store_out<OutT>(g.D, (long long)m * g.d_sm + (long long)n * g.d_sn, acc[m] * g.alpha);
+            for (int j = 0; j < CH; ++j)
+              if (c0 + j < g.M) finish(c0 + j, acc[j]);
+          }
         }
       } else {
         // partial sum: slot 0 for the first row-block of this CTA's run, slot 1 for the last
         const int slot = (tile == (int)(u_begin / g.k_blocks)) ? 0 : 1;
         float* mine = g.partials + ((long long)blockIdx.x * 2 + slot) * (NX * 128);
+#pragma unroll 1
+        for (int c0 = 0; c0 < NX; c0 += CH) {
+          float acc[CH];
+          load_chunk(c0, acc);
 #pragma unroll
-        for (int m = 0; m < NX; ++m) __stcg(&mine[m * 128 + n_local], acc[m]);
+          for (int j = 0; j < CH; ++j)
+            if (c0 + j < g.M) __stcg(&mine[(c0 + j) * 128 + n_local], acc[j]);
+        }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int c_first = owner_of(tile_begin, g.units, grid);
@@ -228,19 +255,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (ticket == c_last - c_first) {
           // last to arrive: every partial of this row-block is in memory; sum in CTA order
           __threadfence();
-          float sum[NX];
+#pragma unroll 1
+          for (int c0 = 0; c0 < g.M; c0 += CH) {
+            float sum[CH];
 #pragma unroll
-          for (int m = 0; m < NX; ++m) sum[m] = 0.f;
-          for (int c = c_first; c <= c_last; ++c) {
-            const int cslot = (tile == (int)(run_start(c, g.units, grid) / g.k_blocks)) ? 0 : 1;
-            const float* theirs = g.partials + ((long long)c * 2 + cslot) * (NX * 128);
+            for (int j = 0; j < CH; ++j) sum[j] = 0.f;
+            for (int c = c_first; c <= c_last; ++c) {
+              const int cslot = (tile == (int)(run_start(c, g.units, grid) / g.k_blocks)) ? 0 : 1;
+              const float* theirs = g.partials + ((long long)c * 2 + cslot) * (NX * 128);
 #pragma unroll
-            for (int m = 0; m < NX; ++m) sum[m] += __ldcg(&theirs[m * 128 + n_local]);
-          }
-          if (n < g.N) {
+              for (int j = 0; j < CH; ++j)
+                if (c0 + j < g.M) sum[j] += __ldcg(&theirs[(c0 + j) * 128 + n_local]);
+            }
+            if (n < g.N) {
 #pragma unroll
-            for (int m = 0; m < NX; ++m)
-              if (m < g.M) store_out<OutT>(g.D, (long long)m * g.d_sm + (long long)n * g.d_sn, sum[m] * g.alpha);
+              for (int j = 0; j < CH; ++j)
+                if (c0 + j < g.M) finish(c0 + j, sum[j]);
+            }
           }
           if (et == 0) g.tickets[tile] = 0;  // ready for the next launch
         }
@@ -290,17 +321,25 @@ static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUt
   return MOYE_OK;
 }
 
+template <int NX>
+static int launch_skinny_out(int out, moye_b200_ctx* h, const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyArgs& a,
+                             cudaStream_t stream) {
+  if (out == MOYE_F32) return launch_skinny_inst<float, NX>(h, tw, tx, a, stream);
+  if (out == MOYE_F16) return launch_skinny_inst<__half, NX>(h, tw, tx, a, stream);
+  return launch_skinny_inst<__nv_bfloat16, NX>(h, tw, tx, a, stream);
+}
+
 int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                        const moye_gemm_params_t* p, cudaStream_t stream) {
   const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
   if (A->dtype != MOYE_F16 && A->dtype != MOYE_BF16)
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "the skinny path takes f16 or bf16 operands");
-  if (M > 32) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "the skinny path needs M <= 32 (got %lld)", (long long)M);
+  if (M > 128) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_SHAPE, "the skinny path needs M <= 128 (got %lld)", (long long)M);
   if (p->beta != 0.f) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the skinny path does not read C (beta must be 0)");
   const int out = D->dtype;
   if (!(out == MOYE_F32 || (out == MOYE_F16 && A->dtype == MOYE_F16) || (out == MOYE_BF16 && A->dtype == MOYE_BF16)))
     MOYE_FAIL(MOYE_ERR_UNSUPPORTED_DTYPE, "output dtype %d not supported for operand dtype %d", out, A->dtype);
-  const int nx = M <= 16 ? 16 : 32;
+  const int nx = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap tw, tx;
   if (int rc = make_tmap_2d(h, &tw, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * 2, 64, 128, true)) return rc;
   if (int rc = make_tmap_2d(h, &tx, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * 2, 64, nx, true)) return rc;
@@ -318,14 +357,14 @@ int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tens
   a.partials = nullptr;
   a.tickets = nullptr;
   a.status = h->d_status;
-  if (nx == 16) {
-    if (out == MOYE_F32) return launch_skinny_inst<float, 16>(h, tw, tx, a, stream);
-    if (out == MOYE_F16) return launch_skinny_inst<__half, 16>(h, tw, tx, a, stream);
-    return launch_skinny_inst<__nv_bfloat16, 16>(h, tw, tx, a, stream);
-  } else {
-    if (out == MOYE_F32) return launch_skinny_inst<float, 32>(h, tw, tx, a, stream);
-    if (out == MOYE_F16) return launch_skinny_inst<__half, 32>(h, tw, tx, a, stream);
-    return launch_skinny_inst<__nv_bfloat16, 32>(h, tw, tx, a, stream);
+  a.act = p->flags & MOYE_EPI_ACT_MASK;
+  a.bias_mode = (p->flags & MOYE_EPI_BIAS_MASK) >> 4;
+  a.bias = a.bias_mode ? p->bias : nullptr;
+  switch (nx) {
+    case 16: return launch_skinny_out<16>(out, h, tw, tx, a, stream);
+    case 32: return launch_skinny_out<32>(out, h, tw, tx, a, stream);
+    case 64: return launch_skinny_out<64>(out, h, tw, tx, a, stream);
+    default: return launch_skinny_out<128>(out, h, tw, tx, a, stream);
   }
 }
 
@@ -437,7 +476,7 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   if (su->num_sms > kStaticMaxSms)
     MOYE_FAIL(MOYE_ERR_TOO_LARGE, "%d SMs exceed the %d the static scratch is sized for", su->num_sms, kStaticMaxSms);
 
-  const int nx = M <= 16 ? 16 : 32;
+  const int nx = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap tw, tx;
   if (int rc = encode_tmap_2d_uncached(&tw, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * 2, 64, 128, true)) return rc;
   if (int rc = encode_tmap_2d_uncached(&tx, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * 2, 64, nx, true)) return rc;
@@ -450,6 +489,9 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   const uint32_t fmt = A->dtype == MOYE_BF16 ? 1u : 0u;
   a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(nx >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.alpha = alpha;
+  a.bias = nullptr;
+  a.bias_mode = 0;
+  a.act = 0;
   a.D = D->ptr;
   a.d_sm = D->stride[0];
   a.d_sn = D->stride[1];

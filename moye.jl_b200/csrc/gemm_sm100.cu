@@ -935,14 +935,21 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   }
 
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
-  if (p.path == 2 && (act != 0 || bias_mode != 0))
-    MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the skinny path has no fused bias / activation; use path 0, 1, 3 or 4");
-  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 32 && N >= 512 && K >= 512 && !a_mn && !b_mn &&
-                      act == 0 && bias_mode == 0))
+  // Automatic choice for decode shapes, from measurements at M = 16 .. 128 (bf16, N x K from 2048 x 8192 to
+  // 28672 x 8192): the stream-K kernel wins only with at most 16 rows and a large weight matrix (16 x 28672 x 8192:
+  // 81 us against 86; 16 x 8192 x 8192: 40 against 44); elsewhere the dense kernel on single CTAs is faster,
+  // provided its tile is narrow enough to spread the one row of tiles over the SMs (below).
+  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && (long long)N * K >= (64ll << 20) &&
+                      !a_mn && !b_mn))
     return launch_gemm_skinny(h, D, A, B, &p, stream);
 
   int bn = p.tile_n;
-  if (bn == 0) bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  if (bn == 0) {
+    bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+    // one row of tiles (M <= 128): 256-wide tiles only if there are enough of them to occupy most SMs; otherwise
+    // 128-wide tiles double the CTAs that stream B (14336 x 4096 weights, M = 64: 29 us against 35.5)
+    if (M <= 128 && bn == 256 && (N + 255) / 256 < (long long)h->num_sms * 2 / 3) bn = 128;
+  }
   // path 4 = CTA pairs on 256 x 512 tiles.  Chosen automatically when it fills the SM pairs at least as well as
   // 256 x 256 tiles do: it needs less operand traffic per flop and measured about 8 % faster on full waves.
   bool wide = p.path == 4;

@@ -242,8 +242,6 @@ def test_fused_epilogue_argument_errors(mb, ho, dev):
         mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, bias=(torch.zeros(7, device=dev), "col"))
     with pytest.raises(mb.MoyeError):
         mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, activation="tanh")
-    with pytest.raises(mb.MoyeError):          # the skinny path has no fused epilogue
-        mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), None, activation="relu", path=2)
     a8, b8, A8, B8, _ = operands(ho, "s8", M, N, K, dev, (5, 6))
     with pytest.raises(mb.MoyeError):          # the integer path stays exact integer arithmetic
         mb.gemm_(mb.MoYeArray(torch.zeros(M, N, device=dev, dtype=torch.int32)), mb.MoYeArray(A8), mb.MoYeArray(B8), None,
@@ -320,7 +318,8 @@ def test_config5_decode_skinny(mb, ho, dev):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 512, 512), (7, 1000, 2048), (16, 1024, 1024), (17, 640, 8192), (32, 4096, 4096),
-                                   (3, 129, 520), (16, 148 * 128, 64)])
+                                   (3, 129, 520), (16, 148 * 128, 64), (33, 1000, 2048), (64, 4096, 4096),
+                                   (100, 640, 8192), (128, 148 * 128, 192), (128, 28672, 1024)])
 def test_skinny_shapes(mb, ho, dev, M, N, K):
     x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
     ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
@@ -329,6 +328,25 @@ def test_skinny_shapes(mb, ho, dev, M, N, K):
         mb.matmul(X, W, Y, path=2, alpha=1.5)
         mb.synchronize_status(dev)
         assert ho.max_rel_err(Y.float().cpu().numpy(), 1.5 * ref) <= 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 1000, 2048), (100, 4096, 1024)])
+def test_skinny_fused_bias_activation(mb, ho, dev, M, N, K):
+    """The stream-K kernel's epilogue applies bias and activation after the partial sums are combined."""
+    x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
+    acc = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    sc = float(np.abs(acc).max())
+    bcol = ho.rng(41).standard_normal(N).astype(np.float32)
+    brow = ho.rng(42).standard_normal(M).astype(np.float32)
+    for which, act in (("col", "gelu"), ("row", "relu"), (None, "silu"), ("col", None)):
+        bias = {None: None, "col": bcol, "row": brow}[which]
+        tb = None if bias is None else (torch.from_numpy(bias).to(dev), which)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            Y = torch.zeros(M, N, dtype=out_dtype, device=dev)
+            mb.gemm_(mb.MoYeArray(Y), mb.MoYeArray(X), mb.MoYeArray(W), None, alpha=1.0 / sc, path=2, bias=tb, activation=act)
+            mb.synchronize_status(dev)
+            want = ho.fused_epilogue(acc, 1.0 / sc, 0.0, None, bias, which, act)
+            assert ho.max_rel_err(Y.float().cpu().numpy(), want) <= 1e-2, (which, act, out_dtype)
 
 
 def test_gemm_argument_errors(mb, dev):
@@ -359,7 +377,8 @@ def test_gemm_argument_errors(mb, dev):
     assert call(A=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1]), B=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1])) == -2
     assert call(p=mb._lib.GemmParams(1.0, 1.0, 1.0, 1.0, 0, 0, 0, 0)) == -1           # beta without C
     assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 96, 0, 0, 0)) == -1          # bad tile_n
-    assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 2, 0)) == -4           # skinny path with M > 32
+    big = T(buf.data_ptr(), F16, [256, 64], [64, 1])
+    assert call(A=big, D=T(out.data_ptr(), F32, [256, 128], [128, 1]), p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 2, 0)) == -4  # skinny path with M > 128
     assert call(D=T(out.data_ptr(), F32, [128, 128], [2, 256])) == -3                 # D without a unit stride
     assert lib.moye_b200_gemm(h, None, ctypes.byref(A), ctypes.byref(B), None, ctypes.byref(p), st) == -1
     A8 = T(buf.data_ptr(), mb._lib.S8, [128, 64], [64, 1])
