@@ -935,13 +935,22 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   }
 
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
-  // Automatic choice for decode shapes, from measurements at M = 16 .. 128 (bf16, N x K from 2048 x 8192 to
-  // 28672 x 8192): the stream-K kernel wins only with at most 16 rows and a large weight matrix (16 x 28672 x 8192:
-  // 81 us against 86; 16 x 8192 x 8192: 40 against 44); elsewhere the dense kernel on single CTAs is faster,
-  // provided its tile is narrow enough to spread the one row of tiles over the SMs (below).
-  if (p.path == 2 || (p.path == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && (long long)N * K >= (64ll << 20) &&
-                      !a_mn && !b_mn))
-    return launch_gemm_skinny(h, D, A, B, &p, stream);
+  // Automatic choice for decode shapes, from measurements at M = 1 .. 128 (bf16, weights from 2048 x 8192 to
+  // 28672 x 8192).  The dense kernel on single CTAs streams one tile per CTA over the whole of K, so it is only as
+  // fast as its row of tiles is wide: with at most 64 tiles (of the width chosen below) and a long K the stream-K
+  // kernel, which deals equal runs to all SMs, wins up to M = 64 (8192 x 8192 weights, M = 32: 34 us against 44;
+  // 4096 x 14336, M = 64: 37 against 70).  With a full row of tiles the two are within a few percent of each other
+  // from M = 8 (28672 x 8192: 78-85 us against 81-86, box to box), and stream-K keeps the cases with very few rows
+  // (M = 1: 75 against 99) and the largest weight matrices at M <= 16.
+  bool use_skinny = p.path == 2;
+  if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 64 && !a_mn && !b_mn && N >= 128 && K >= 512) {
+    const long long nk = (long long)N * K;
+    const long long tiles256 = (N + 255) / 256;
+    const long long tiles = tiles256 >= (long long)h->num_sms * 2 / 3 ? tiles256 : (N + 127) / 128;
+    use_skinny = (M <= 16 && nk >= (64ll << 20)) || (tiles <= 64 && K >= 4096) ||
+                 (M <= 16 && tiles <= 64 && K >= 1024 && nk >= (8ll << 20)) || (M <= 4 && nk >= (8ll << 20));
+  }
+  if (use_skinny) return launch_gemm_skinny(h, D, A, B, &p, stream);
 
   int bn = p.tile_n;
   if (bn == 0) {
