@@ -187,6 +187,35 @@ def cpu_reference_rate(ho, np, M, N, K, seconds, threads):
     return 2.0 * rows * N * K / dt / 1e12, rows, dt, (tr, tc)
 
 
+def cpu_other_configs(ho, np, threads):
+    """The reference's own CPU-runnable cases, timed on the host cores beside the headline baseline: configuration 1
+    (256^3 fp32 through the emulated `matmul_kernel` and the plain host gemm!, one thread, and the threaded host GEMM)
+    and the copy kernel of configuration 2 on a 2048 x 2048 fp16 slice."""
+    out = {}
+    M = N = K = 256
+    A, B = ho.uniform_pm1(0, (M * K,)), ho.uniform_pm1(1, (N * K,))
+    t0 = time.perf_counter()
+    ho.matmul_kernel_f32(A, B, M, N, K)
+    out["cfg1_matmul_kernel_emulated_1thread_GFLOP/s"] = 2.0 * M * N * K / (time.perf_counter() - t0) / 1e9
+    t0 = time.perf_counter()
+    ho.gemm_f32(A, (1, M), B, (1, N), M, N, K)
+    out["cfg1_host_gemm_1thread_GFLOP/s"] = 2.0 * M * N * K / (time.perf_counter() - t0) / 1e9
+    tr = 1
+    while tr * tr * 4 <= threads:
+        tr *= 2
+    tc = max(1, threads // tr)
+    t0 = time.perf_counter()
+    ho.matmul_threads_f32(A, B, M, N, K, thread_layout=(tr, tc))
+    out[f"cfg1_host_gemm_{tr * tc}threads_GFLOP/s"] = 2.0 * M * N * K / (time.perf_counter() - t0) / 1e9
+    m = n = 2048
+    src = ho.uniform_pm1_f16_bits(2, (m * n,))
+    dst = np.zeros_like(src)
+    t0 = time.perf_counter()
+    ho.copy_kernel(dst, src, m, n, bm=128, bn=64, tm=16, tn=16)
+    out["cfg2_copy_kernel_2048x2048_f16_1thread_GB/s"] = 2.0 * m * n * 2 / (time.perf_counter() - t0) / 1e9
+    return out
+
+
 def run_reference_arm(args):
     rank, _, world = dist_env()
     if rank != 0:
@@ -406,7 +435,8 @@ def run_ours(args):
         line["cpu_baseline"] = {
             "value": val, "unit": "TFLOP/s", "cores": tl[0] * tl[1], "kind": "port",
             "sample": f"first {rows} of {M} rows of C (N={N}, K={K}), fp32 inputs widened, threaded host gemm with "
-                      f"thread layout {tl}, {dt:.1f} s"}
+                      f"thread layout {tl}, {dt:.1f} s",
+            "other_configs": cpu_other_configs(ho, np, threads)}
     if rank == 0 and world == 1 and not args.no_extras:
         line["also"] = extras(mb, torch, dev, peaks)
     if rank == 0:
