@@ -146,6 +146,13 @@ const char* moye_b200_last_error(void);
  * (reference test/device/matmul.jl:80). */
 int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
 
+/* Integration test of the error path: launches a one-warp kernel that waits, with the bounded wait every
+ * kernel of the library uses, on an mbarrier nothing arrives at.  The wait gives up after its poll limit
+ * (about two seconds), the kernel returns normally, and the next moye_b200_status() on the stream
+ * reports MOYE_ERR_TIMEOUT with site code 901; the context stays usable.  No counterpart in the reference
+ * (its kernels have no waits that can fail). */
+int moye_b200_selftest_bounded_wait(moye_handle_t h, void* stream);
+
 /* D = alpha*scale_a*scale_b * A.B^T + beta*C with A:(M,K), B:(N,K), C,D:(M,N).
  * Takes over the whole `matmul_kernel` of reference examples/gemm.jl:4-64 (the gemm!-based
  * form is test/device/matmul.jl:3-53): local_tile of A/B/C, the gmem->smem `copyto!`

@@ -65,6 +65,7 @@ EXPORTS = {
     "moye_b200_version": (ctypes.c_int, []),
     "moye_b200_last_error": (ctypes.c_char_p, []),
     "moye_b200_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]),
+    "moye_b200_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "moye_b200_gemm": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
                                       ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.POINTER(GemmParams),
                                       ctypes.c_void_p]),

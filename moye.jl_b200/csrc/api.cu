@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "common.h"
+#include "ptx.cuh"
 
 namespace moye {
 
@@ -148,6 +149,20 @@ static int check_handle(moye_b200_ctx* h) {
 
 using namespace moye;
 
+namespace moye {
+// One warp waits, with the same bounded wait every kernel of the library uses, on an mbarrier that nothing ever
+// arrives at.  The wait gives up after its poll limit, records the site code and the kernel returns normally.
+__global__ void bounded_wait_probe_kernel(int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, status, 901);
+}
+}  // namespace moye
+
 extern "C" {
 
 int moye_b200_version(void) { return MOYE_B200_VERSION; }
@@ -204,6 +219,13 @@ int moye_b200_status(moye_handle_t h, void* stream, int32_t* site) {
     MOYE_CUDA(cudaMemset(h->d_status, 0, sizeof(int)));
     MOYE_FAIL(MOYE_ERR_TIMEOUT, "a bounded device-side wait ran out (site code %d)", v);
   }
+  return MOYE_OK;
+}
+
+int moye_b200_selftest_bounded_wait(moye_handle_t h, void* stream) {
+  if (int rc = check_handle(h)) return rc;
+  moye::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(h->d_status);
+  MOYE_CUDA(cudaGetLastError());
   return MOYE_OK;
 }
 

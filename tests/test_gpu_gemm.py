@@ -168,6 +168,26 @@ def test_examples_gemm_jl_float32(mb, ho, dev):
     assert np.all(np.abs(got - raw) <= 2.0 ** -9 * bound)
 
 
+def test_config1_fp32_against_committed_golden(mb, ho, dev):
+    """Configuration 1 as the reference runs it on its host path (256 x 256 x 256 Float32, column-major, seeds 0 / 1;
+    test/host/tiling_matmul.jl:20-41), on the device: within the tf32 input truncation of the committed fp32 golden,
+    and like every float kind against the oracle on the truncated operands."""
+    M = N = K = 256
+    a, b = ho.uniform_pm1(0, (M * K,)), ho.uniform_pm1(1, (N * K,))
+    gold = np.load(os.path.join(GOLD, "cfg1_host_gemm_f32_256.npz"))["C"]          # (M, N), fp32 sequential-k host gemm!
+    A = mb.MoYeArray(torch.from_numpy(a).to(dev), mb.make_layout((M, K)))
+    B = mb.MoYeArray(torch.from_numpy(b).to(dev), mb.make_layout((N, K)))
+    for path in (1, 3, 0):
+        cbuf = torch.zeros(M * N, device=dev)
+        mb.matmul(A, B, mb.MoYeArray(cbuf, mb.make_layout((M, N))), path=path)
+        mb.synchronize_status(dev)
+        got = cbuf.cpu().numpy().reshape(N, M).T
+        bound = ho.gemm_f32(np.abs(a), (1, M), np.abs(b), (1, N), M, N, K).reshape(N, M).T
+        assert np.all(np.abs(got - gold) <= 2.0 ** -9 * bound), path
+        want = ho.gemm_f32(ho.tf32_trunc(a), (1, M), ho.tf32_trunc(b), (1, N), M, N, K).reshape(N, M).T
+        assert ho.max_rel_err(got, want) <= TOL["f32"], path
+
+
 def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
     M, N, K = 256, 384, 512
     a, b, A, B, dt = operands(ho, "f16", M, N, K, dev, (3, 4))
@@ -432,3 +452,22 @@ def test_host_pipeline_steps_are_each_correct(mb, ho, dev):
     mb.synchronize_status(dev)
     for hC, ref in zip(outs, refs):
         assert ho.max_rel_err(hC.numpy()[::5], ref) <= 1e-2
+
+
+def test_bounded_wait_gives_up_and_the_context_survives(mb, ho, dev):
+    """The error path of every kernel's waits, end to end: a wait on a barrier nothing arrives at runs out, the
+    kernel returns, `moye_b200_status` reports TIMEOUT with the site code once, and the next launches work."""
+    lib, h = mb._lib.load(), mb._lib.handle(dev.index)
+    st = mb.current_stream_ptr(dev)
+    assert lib.moye_b200_selftest_bounded_wait(h, st) == 0
+    site = ctypes.c_int32(0)
+    assert lib.moye_b200_status(h, st, ctypes.byref(site)) == -7 and site.value == 901
+    assert b"bounded" in lib.moye_b200_last_error()
+    assert lib.moye_b200_status(h, st, ctypes.byref(site)) == 0 and site.value == 0      # reported once, then clear
+    M, N, K = 256, 512, 256
+    a, b, A, B, dt = operands(ho, "f16", M, N, K, dev, (3, 4))
+    C = torch.zeros(M, N, device=dev)
+    mb.matmul(A, B, C)
+    mb.synchronize_status(dev)
+    ref = ho.gemm_samples(a, b, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    assert ho.max_rel_err(C.cpu().numpy(), ref) <= 1e-2
