@@ -270,6 +270,40 @@ def test_fused_epilogue_argument_errors(mb, ho, dev):
     mb.synchronize_status(dev)
 
 
+def widen(ho, x, kind):
+    """Raw operand values as the oracle widens them (exact)."""
+    if kind == "f16":
+        return ho.half_to_float(x)
+    if kind == "bf16":
+        return ho.bf16_to_float(x)
+    if kind == "e4m3":
+        return ho.e4m3_to_float(x)
+    return x
+
+
+def checksum_check(ho, kind, a, b, C, M, N, K, scale, tol):
+    """A checksum over every element of C, computed on the host without a GPU library: the row sums of C must equal
+    A . (sum over n of B[n, :]) -- exactly for s8 (int64); for the float kinds within 8 standard deviations of the
+    output rounding (eps_out * sqrt(sum C^2)) plus 1e-5 * sum |C| for the fp32 accumulation order, which is far
+    below what one wrong 32-column chunk of a row would change."""
+    wide = np.int64 if kind == "s8" else np.float64
+    bsum = np.zeros(K, dtype=wide)
+    for n0 in range(0, N, 1024):
+        bsum += widen(ho, b[n0 * K:(n0 + 1024) * K], kind).reshape(-1, K).astype(wide).sum(axis=0)
+    want = np.empty(M, dtype=wide)
+    for m0 in range(0, M, 1024):
+        want[m0:m0 + 1024] = widen(ho, a[m0 * K:(m0 + 1024) * K], kind).reshape(-1, K).astype(wide) @ bsum
+    if kind == "s8":
+        assert np.array_equal(C.sum(dim=1, dtype=torch.int64).cpu().numpy(), want)
+    else:
+        Cd = C.double()
+        got = Cd.sum(dim=1).cpu().numpy()
+        eps = {torch.float32: 2.0 ** -24, torch.bfloat16: 2.0 ** -9, torch.float16: 2.0 ** -11}[C.dtype]
+        bound = 8.0 * eps * (Cd * Cd).sum(dim=1).sqrt().cpu().numpy() + 1e-5 * Cd.abs().sum(dim=1).cpu().numpy()
+        del Cd
+        assert np.all(np.abs(got - want * float(scale)) <= bound)
+
+
 def sampled_check(mb, ho, dev, kind, M, N, K, seeds, out_dtype, tol, nsample=128, **kw):
     a, b, A, B, dt = operands(ho, kind, M, N, K, dev, seeds)
     C = torch.zeros(M, N, dtype=out_dtype, device=dev)
@@ -288,6 +322,7 @@ def sampled_check(mb, ho, dev, kind, M, N, K, seeds, out_dtype, tol, nsample=128
     else:
         assert ho.max_rel_err(got_r.float().numpy(), ref_r * scale) <= tol
         assert ho.max_rel_err(got_c.float().numpy(), ref_c * scale) <= tol
+    checksum_check(ho, kind, a, b, C, M, N, K, scale, tol)
     return A, B, C
 
 
