@@ -106,10 +106,12 @@ typedef struct {
   float scale_b;
   int32_t tile_n;                /* CTA tile N: 0 (auto), 64, 128 or 256; tile M is 128.  Widened to 128 (256 on
                                     CTA pairs) when B is MN-major with 8-bit elements */
-  int32_t split_k;               /* skinny path only: 0 = auto */
+  int32_t split_k;               /* path 5: CTAs per output tile (2, 4 or 8; 0 = auto); ignored elsewhere */
   int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel (M <= 128),
                                     3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
-                                    4 CTA pairs on 256 x 512 tiles */
+                                    4 CTA pairs on 256 x 512 tiles,
+                                    5 split-K on thread-block clusters: 128 x tile_n tiles, `split_k` CTAs per tile
+                                    reduce through distributed shared memory (for outputs with few tiles) */
   int32_t flags;                 /* fused epilogue: MOYE_EPI_* activation | MOYE_EPI_BIAS_*; 0 = plain GEMM */
   const float* bias;             /* device pointer, fp32, read only when a bias mode is set */
 } moye_gemm_params_t;

@@ -147,12 +147,14 @@ def _epilogue(bias, activation, D, dev):
 
 
 def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None, bias=None,
-          activation=None):
+          activation=None, split_k=0):
     """`gemm!([tiled_mma,] D, A, B, C)`: D = alpha*scale_a*scale_b * A.B^T + beta*C with
     A:(M,K), B:(N,K), C and D:(M,N) in global memory.  `gemm_(A, B, C)` is `gemm!(C, A, B, C)`
     like the reference's three-argument form (src/algorithm/blas.jl:11).  `bias` (float32, one
     value per column or per row of D) and `activation` ("relu", "gelu", "silu") are fused into the
-    epilogue: D = act(alpha*... + beta*C + bias), in fp32 before the output conversion."""
+    epilogue: D = act(alpha*... + beta*C + bias), in fp32 before the output conversion.  `path` picks the
+    kernel (0: the library chooses; 1 single CTAs, 2 stream-K, 3 CTA pairs, 4 pairs on 256x512 tiles, 5 split-K on
+    clusters with `split_k` = 2, 4 or 8 CTAs per tile)."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
         tiled_mma, args = args[0], args[1:]
@@ -176,7 +178,7 @@ def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0
     lib, h = _lib.load(), _lib.handle(dev.index)
     st = stream if stream is not None else current_stream_ptr(dev)
     flags, bias_ptr, _ = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
-    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, flags, bias_ptr)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, split_k, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if (C is not None and beta != 0.0) else None
     _lib.check(lib.moye_b200_gemm(h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB),
@@ -224,7 +226,8 @@ class LaunchPlan:
             _lib.check(rc)
 
 
-def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, bias=None, activation=None):
+def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, bias=None, activation=None,
+              split_k=0):
     """`gemm_` with the argument marshalling done once; returns a `LaunchPlan`."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
@@ -246,7 +249,7 @@ def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, pa
         tile_n = tile_n or op.shape_mnk[1]
     lib, h = _lib.load(), _lib.handle(dev.index)
     flags, bias_ptr, bias = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
-    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, 0, path, flags, bias_ptr)
+    p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, split_k, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if use_c else None
     argv = (h, ctypes.byref(tD), ctypes.byref(tA), ctypes.byref(tB), ctypes.byref(tC) if use_c else None,

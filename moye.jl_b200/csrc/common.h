@@ -77,6 +77,7 @@ struct moye_b200_ctx {
   std::mutex mu;
   std::unordered_map<moye::TmapKey, CUtensorMap, moye::TmapKeyHash> tmaps;
   std::unordered_set<const void*> configured;   // kernels whose dynamic-smem limit is already raised
+  std::unordered_map<uint64_t, int> cluster_fit; // (kernel, cluster size) -> clusters the device can hold at once
 };
 
 namespace moye {

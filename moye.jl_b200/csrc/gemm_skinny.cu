@@ -188,6 +188,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // The accumulator is drained in chunks of CH columns (= rows of X) so that NX up to 128 needs no more
       // registers than NX = 32; the accumulator buffer is handed back after the last chunk has been read.
       constexpr int CH = NX < 32 ? NX : 32;
+      const int last_c0 = ((g.M - 1) / CH) * CH;  // chunks past the M rows of X hold padding and are not read
       const int n_local = q * 32 + lane;
       const int n = tile * 128 + n_local;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * NX;
@@ -205,7 +206,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(v[j]);
         }
-        if (c0 + CH == NX) {
+        if (c0 == last_c0) {
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -258,14 +259,34 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       };
       if (whole) {
+        // These warps run alone on their schedulers, so every instruction costs its full latency: the common case
+        // (no activation, no per-row bias) is a multiply-add, a conversion, a store and a pointer step per row.
+        const bool plain = g.act == 0 && g.bias_mode != 2;
+        OutT* drow = reinterpret_cast<OutT*>(g.D) + (long long)n * g.d_sn;
+        const long long dstep = g.d_sm;
+        const float alpha = g.alpha;
 #pragma unroll 1
-        for (int c0 = 0; c0 < NX; c0 += CH) {
+        for (int c0 = 0; c0 <= last_c0; c0 += CH) {
           float acc[CH];
           load_chunk(c0, acc);
           if (n < g.N) {
+            if (plain) {
+              OutT* p = drow + (long long)c0 * dstep;
+              const int left = g.M - c0;
 #pragma unroll
-            for (int j = 0; j < CH; ++j)
-              if (c0 + j < g.M) finish(c0 + j, acc[j]);
+              for (int j = 0; j < CH; ++j) {
+                if (j < left) {
+                  if constexpr (sizeof(OutT) == 4) *reinterpret_cast<float*>(p) = fmaf(acc[j], alpha, bias_n);
+                  else if constexpr (std::is_same<OutT, __half>::value) *p = __float2half_rn(fmaf(acc[j], alpha, bias_n));
+                  else *p = __float2bfloat16_rn(fmaf(acc[j], alpha, bias_n));
+                }
+                p += dstep;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < CH; ++j)
+                if (c0 + j < g.M) finish(c0 + j, acc[j]);
+            }
           }
         }
       } else {
@@ -273,7 +294,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int slot = (tile == (int)(u_begin / g.k_blocks)) ? 0 : 1;
         float* mine = g.partials + ((long long)blockIdx.x * 2 + slot) * (NX * 128);
 #pragma unroll 1
-        for (int c0 = 0; c0 < NX; c0 += CH) {
+        for (int c0 = 0; c0 <= last_c0; c0 += CH) {
           float acc[CH];
           load_chunk(c0, acc);
 #pragma unroll

@@ -207,6 +207,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_remote(uint32_t cluster_ad
                "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// 128-bit load from the shared memory of any CTA of the cluster (address from mapa_shared).
+__device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // TMA load whose completion is counted on an mbarrier of the CTA pair's leader (`mbar_cluster_addr`

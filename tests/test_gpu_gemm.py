@@ -232,7 +232,8 @@ def test_fused_bias_activation_epilogue(mb, ho, dev, kind, out):
     tol = {torch.float32: TOL[kind], torch.bfloat16: max(TOL[kind], 1e-2)}[out]
     cases = [(1, 256, False, "col", "relu", 0.0), (1, 64, True, "row", "gelu", 0.0), (3, 256, False, "row", "silu", 0.5),
              (3, 128, True, "col", None, 0.0), (4, 0, False, "col", "gelu", 0.0), (4, 0, True, "row", "relu", 1.0),
-             (0, 0, False, None, "silu", 0.0), (0, 0, False, "col", None, 2.0)]
+             (0, 0, False, None, "silu", 0.0), (0, 0, False, "col", None, 2.0), (5, 0, False, "col", "gelu", 0.5),
+             (5, 128, True, "row", "relu", 0.0)]
     for path, tile_n, m_major, which, act, beta in cases:
         if m_major and (M * torch.empty(0, dtype=out).element_size()) % 16:
             continue
