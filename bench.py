@@ -55,6 +55,8 @@ WORKLOADS = {
     "gemm_f16_9472x4096x2048": ("f16", 9472, 4096, 2048, "f32"),
     # Float32 storage on the tf32 tensor-core kind, column-major like examples/gemm.jl (its literal element type)
     "gemm_f32_8192_colmajor": ("f32", 8192, 8192, 8192, "f32"),
+    # a few hundred rows against a mid-sized weight matrix: 32 output tiles, the case of the split-K cluster kernel
+    "gemm_bf16_256x4096x4096": ("bf16", 256, 4096, 4096, "bf16"),
 }
 
 
@@ -267,7 +269,8 @@ def workload_config(name, gpus):
     return {"workload": name, "M_per_gpu": M, "N": N, "K": K, "global_M": M * gpus,
             "layout": "A,B,D column-major (MN-major, as examples/gemm.jl)" if name.endswith("_colmajor") else "A,B K-major (TN); D row-major",
             "in": kind, "out": out, "sharding": f"M-sharded x{gpus}, B replicated, no collective",
-            "l2": "operands+output exceed the 126 MB L2 (no flush needed)" if M * K + N * K > 64e6 else "rotating buffers"}
+            "l2": "operands+output exceed the 126 MB L2 (no flush needed)" if M * K + N * K > 64e6
+            else "operand/output buffer sets rotated, more than 512 MB in total"}
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -305,14 +308,26 @@ def run_ours(args):
     if kind in ("copy", "transpose"):
         return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier, transpose=kind == "transpose")
 
-    A, B, C = make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank, colmajor=name.endswith("_colmajor"))
+    # operands that would sit in the 126 MB L2 are rotated over enough buffer sets to exceed it several times
+    rotate = not (M * K + N * K > 64e6)
+    set_bytes = 0
+    sets = []
+    while True:
+        sets.append(make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank + 16 * len(sets),
+                                  colmajor=name.endswith("_colmajor")))
+        set_bytes += sum(t.numel() * t.element_size() for t in sets[-1])
+        if not rotate or set_bytes > 512e6:
+            break
+    A, B, C = sets[0]
     kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
-    mA, mB, mC = mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(C)
-    plan = mb.plan_gemm(mC, mA, mB, None, **kw)   # the argument marshalling of gemm_ done once
+    plans = [mb.plan_gemm(mb.MoYeArray(c), mb.MoYeArray(a), mb.MoYeArray(b), None, **kw) for a, b, c in sets]
+    plan = plans[0]                               # the argument marshalling of gemm_ done once per buffer set
     stream_ptr = mb.current_stream_ptr(dev)
+    turn = [0]
 
     def step():
-        plan(stream_ptr)
+        turn[0] += 1
+        plans[turn[0] % len(plans)](stream_ptr)
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -335,7 +350,7 @@ def run_ours(args):
     ms_max = float(t.item())
     total_flops = flops_of(kind, M, N, K) * world
     value = total_flops / (ms_max * 1e-3) / 1e12
-    bytes_bound = kind == "bf16" and M <= 32
+    bytes_bound = kind == "bf16" and M <= 512
 
     # end to end: pinned host operands -> device -> GEMM -> pinned host result, every step, through the
     # package's host pipeline (copies and kernel on three streams over two device buffer sets)
@@ -406,7 +421,8 @@ def run_ours(args):
                 "serial_ms_per_step": e2e_serial_ms},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_kind}, of {peak_src}",
-                     "kernel": "gemm_tcgen05_2cta_wide_kernel" if not bytes_bound else "gemm_skinny_kernel",
+                     "kernel": ("gemm_tcgen05_2cta_wide_kernel" if not bytes_bound else
+                                ("gemm_skinny_kernel" if M <= 16 else "gemm_tcgen05_splitk_kernel")),
                      "kernel_ms": ms},
     }
     if dist is not None and world > 1 and not args.no_extras and not bytes_bound:
@@ -451,9 +467,10 @@ def extras(mb, torch, dev, peaks):
     out = {}
     stream = torch.cuda.current_stream()
     for name in ("gemm_f16_4096", "gemm_f16_8192_colmajor", "gemm_bf16_8192", "gemm_f32_8192_colmajor",
-                 "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192"):
+                 "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192",
+                 "gemm_bf16_256x4096x4096"):
         kind, M, N, K, o = WORKLOADS[name]
-        nset = 3 if M <= 32 else 1  # rotate weight buffers for the HBM-bound decode shape
+        nset = 3 if M <= 32 else (12 if M <= 512 else 1)  # rotate weight buffers for the HBM-bound shapes
         sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i, colmajor=name.endswith("_colmajor"))
                 for i in range(nset)]
         kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
@@ -466,9 +483,10 @@ def extras(mb, torch, dev, peaks):
             plans[i[0] % nset](sp)
 
         ms = time_launches(torch, fn, 20, 5, stream)
-        if M <= 32:
+        if M <= 512:
             nbytes = (M * K + N * K + M * N) * 2
-            out[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+            out[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                         "TFLOP/s": 2.0 * M * N * K / ms / 1e9}
         else:
             out[name] = {"ms": ms, "TFLOP/s": 2.0 * M * N * K / ms / 1e9}
         del sets, plans

@@ -1250,18 +1250,18 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
   // Automatic choice for decode shapes, from measurements at M = 1 .. 128 (bf16, weights from 2048 x 8192 to
   // 28672 x 8192).  The dense kernel on single CTAs streams one tile per CTA over the whole of K, so it is only as
-  // fast as its row of tiles is wide: with at most 64 tiles (of the width chosen below) and a long K the stream-K
-  // kernel, which deals equal runs to all SMs, wins up to M = 64 (8192 x 8192 weights, M = 32: 34 us against 44;
-  // 4096 x 14336, M = 64: 37 against 70).  With a full row of tiles the two are within a few percent of each other
-  // from M = 8 (28672 x 8192: 78-85 us against 81-86, box to box), and stream-K keeps the cases with very few rows
-  // (M = 1: 75 against 99) and the largest weight matrices at M <= 16.
+  // fast as its row of tiles is wide.  The stream-K kernel deals equal runs of (row-block, K-block) units to all
+  // SMs; it is the fastest form up to 16 rows (X tiles of 2 KB): on the largest weights (16 x 28672 x 8192: 77 us
+  // against 81-86), wherever the row of tiles is short, and with very few rows (M = 1 at 28672 x 8192: 75 against
+  // 99).  From 17 rows its X tiles and its epilogue grow with M and the split-K kernel (below) or the dense
+  // kernel take over (4096 x 4096 weights, M = 64: 16.6 us split-K, 25 stream-K, 25 dense).
   bool use_skinny = p.path == 2;
-  if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 64 && !a_mn && !b_mn && N >= 128 && K >= 512) {
+  if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && !a_mn && !b_mn && N >= 128 && K >= 512) {
     const long long nk = (long long)N * K;
     const long long tiles256 = (N + 255) / 256;
     const long long tiles = tiles256 >= (long long)h->num_sms * 2 / 3 ? tiles256 : (N + 127) / 128;
-    use_skinny = (M <= 16 && nk >= (64ll << 20)) || (tiles <= 64 && K >= 4096) ||
-                 (M <= 16 && tiles <= 64 && K >= 1024 && nk >= (8ll << 20)) || (M <= 4 && nk >= (8ll << 20));
+    use_skinny = (M <= 16 && nk >= (64ll << 20)) || (M <= 16 && tiles <= 64 && K >= 1024 && nk >= (8ll << 20)) ||
+                 (M <= 4 && nk >= (8ll << 20));
   }
   if (use_skinny) return launch_gemm_skinny(h, D, A, B, &p, stream);
 
@@ -1286,22 +1286,37 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   }
   if (wide) bn = 256;
   // path 5 = split-K on clusters (128 x tile_n tiles, `split_k` CTAs per tile).  Chosen automatically when the
-  // output has so few tiles that even single CTAs on 128-row tiles would leave most SMs idle, and K is long
-  // enough to cut: the largest of 8, 4, 2 CTAs per tile that keeps tiles x split within the SM count.
+  // output has so few tiles that the other kernels would leave most SMs idle and K is long enough to cut (at least
+  // 8 blocks per CTA): the tile width (256, 128) and split (4, 2) that put the most CTAs on the SMs without
+  // exceeding them (4096 x 4096 weights, M = 128: 16.7 us with 32 tiles x 4 against 25-27 unsplit; M = 512: 27
+  // against 31).  Clusters of 8 measured slower than clusters of 4 with the same number of CTAs and are only used
+  // on request.
   const int kb_total = (int)((K + 128 / dtype_bytes(A->dtype) - 1) / (128 / dtype_bytes(A->dtype)));
   int split = 0;
+  if (p.path == 5) {
+    if (p.split_k != 0 && p.split_k != 2 && p.split_k != 4 && p.split_k != 8)
+      MOYE_FAIL(MOYE_ERR_INVALID_ARG, "split_k must be 0, 2, 4 or 8 (got %d)", p.split_k);
+    if (p.tile_n != 0 && p.tile_n != 128 && p.tile_n != 256)
+      MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the split-K path takes tile_n 0, 128 or 256 (got %d)", p.tile_n);
+  }
   if (p.path == 5 || (p.path == 0 && !wide && p.tile_n == 0)) {
-    const int bn_s = p.path == 5 && p.tile_n ? p.tile_n : (N > 128 ? 256 : 128);
-    const long long tiles_s = ((M + 127) / 128) * ((N + bn_s - 1) / bn_s);
-    if (p.path == 5 && p.split_k != 0) {
-      if (p.split_k != 2 && p.split_k != 4 && p.split_k != 8) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "split_k must be 0, 2, 4 or 8 (got %d)", p.split_k);
-      split = p.split_k;
-    } else {
-      for (int sp = 8; sp >= 2; sp /= 2)
-        if (tiles_s * sp <= h->num_sms && kb_total >= 8 * sp) { split = sp; break; }
-      if (p.path == 5 && split == 0) split = 2;
+    long long best_ctas = 0;
+    for (int bn_c = 256; bn_c >= 128; bn_c /= 2) {
+      if (p.tile_n != 0 && bn_c != p.tile_n) continue;
+      if (bn_c == 256 && N <= 128) continue;
+      const long long tiles_c = ((M + 127) / 128) * ((N + bn_c - 1) / bn_c);
+      for (int sp = 4; sp >= 2; sp /= 2) {
+        if (p.split_k != 0 && sp != p.split_k) continue;
+        if (tiles_c * sp <= h->num_sms && kb_total >= 8 * sp) {
+          if (tiles_c * sp > best_ctas) { best_ctas = tiles_c * sp; split = sp; bn = bn_c; }
+          break;
+        }
+      }
     }
-    if (split) bn = bn_s;
+    if (p.path == 5 && split == 0) {  // asked for explicitly: honour it even where it is not the fast choice
+      split = p.split_k ? p.split_k : 2;
+      bn = p.tile_n ? p.tile_n : (N > 128 ? 256 : 128);
+    }
   }
   const bool pair = !split && (wide || p.path == 3 || (p.path == 0 && M > 128 && bn >= 128));
   if (pair && bn < 128) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "CTA pairs take tile_n 128 or 256 (got %d)", bn);
