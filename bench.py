@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM traffic of one launch of the 8192^3 fp16 GEMM kernel (dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu captures summarised under profiles/), bytes per launch.
-NCU_TRAFFIC_BYTES = {"gemm_f16_8192": 0.9137e9 + 0.2436e9,     # profiles/gemm_tcgen05_2cta_wide_f16_8192_dram_traffic.txt
+NCU_TRAFFIC_BYTES = {"gemm_f16_8192": 0.8291e9 + 0.2346e9,     # profiles/gemm_tcgen05_2cta_wide_f16_8192_dram_traffic.txt
                      "decode_bf16_16x28672x8192": 471.24e6 + 6.1e6,  # profiles/gemm_skinny_bf16_16x28672x8192.txt
                      "gemm_f16_4096x8192x4096": 179.6e6 + 100.5e6}
 
