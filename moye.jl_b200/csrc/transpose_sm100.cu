@@ -4,12 +4,12 @@
 // Reference counterpart: `transpose_kernel` (test/host/copy_async.jl:51-74: @tile of both arrays, copyto!
 // gmem->smem through a (32,32):(1,33) padded tile, `MoYe.transpose` of the shared tile, copyto! smem->gmem).
 //
-// Here a stage of 16V rows x 8V*NB columns (V = 16 / sizeof(T) elements per 128-bit vector; 16 KB, 32 KB for
-// 1-byte elements) arrives by TMA in the 128-byte swizzle, 128 threads each turn V x V element blocks in registers
+// Here a stage of 8V rows x 8V*NB columns (V = 16 / sizeof(T) elements per 128-bit vector; 8 KB, 16 KB for
+// 1-byte elements) arrives by TMA in the 128-byte swizzle, 64 threads each turn V x V element blocks in registers
 // (V 128-bit reads along the source rows, V 128-bit writes along the destination rows) into a second swizzled
 // tile, and TMA stores it.  The thread -> block map walks diagonals, which makes every 8-lane phase of both the
-// reads and the writes touch 8 distinct 16-byte bank groups: no padding, no bank conflicts.  Loads run two
-// stages ahead of the stores.  Ragged edges need no code: TMA zero-fills loads and clips stores.
+// reads and the writes touch 8 distinct 16-byte bank groups: no padding, no bank conflicts.  Loads run one
+// stage ahead of the stores, four CTAs per SM.  Ragged edges need no code: TMA zero-fills loads and clips stores.
 // HBM-bound: algorithmic traffic is one read plus one write of the tensor.
 #include "common.h"
 #include "ptx.cuh"
@@ -67,24 +67,25 @@ __device__ __forceinline__ void transpose_block(const uint4 (&in)[16 / E], uint4
   }
 }
 
-template <int E>
+template <int E, int SLOTS_ = 2, int NB_ = 0, int RM_ = 1>
 struct TransposeCfg {
+  static constexpr int RM = RM_;                       // square 8V x 8V sub-tiles along m per stage (1 or 2)
   static constexpr int V = 16 / E;                     // elements per 128-bit vector = block edge
-  static constexpr int NB = (8 / V) > 0 ? (8 / V) : 1; // input boxes per stage
-  static constexpr int ROWS = 16 * V;                  // source rows (m) per stage
+  static constexpr int NB = NB_ ? NB_ : ((8 / V) > 0 ? (8 / V) : 1); // input boxes per stage: 8 KB stages (16 KB for 1-byte elements)
+  static constexpr int ROWS = 8 * V * RM_;             // source rows (m) per stage
   static constexpr int COLS = 8 * V * NB;              // source columns (n) per stage
   static constexpr int IN_BOX = ROWS * 128;            // bytes of one input box {8V, 16V}
   static constexpr int STAGE = IN_BOX * NB;
-  static constexpr int OUT_HALF = STAGE / 2;           // bytes of one output box {8V, 8V*NB}
-  static constexpr int SLOTS = 3, LOOK = 2;
+  static constexpr int OUT_HALF = STAGE / RM_;         // bytes of one output box {8V, 8V*NB}
+  static constexpr int SLOTS = SLOTS_, LOOK = SLOTS_ - 1;
   static constexpr int SMEM = (SLOTS + 2) * STAGE + SLOTS * 8 + 1024;
 };
 
-template <int E>
-__global__ void __launch_bounds__(128) transpose_tma_kernel(const __grid_constant__ CUtensorMap tmS,
+template <int E, int SLOTS_ = 2, int NB_ = 0, int RM_ = 1>
+__global__ void __launch_bounds__(64 * RM_) transpose_tma_kernel(const __grid_constant__ CUtensorMap tmS,
                                                             const __grid_constant__ CUtensorMap tmD,
                                                             const TransposeArgs a) {
-  using Cfg = TransposeCfg<E>;
+  using Cfg = TransposeCfg<E, SLOTS_, NB_, RM_>;
   constexpr int V = Cfg::V, NB = Cfg::NB, STAGE = Cfg::STAGE, SLOTS = Cfg::SLOTS, LOOK = Cfg::LOOK;
   static_assert(SLOTS == LOOK + 1, "the slot refilled in iteration i is the one consumed in iteration i - 1");
   extern __shared__ uint8_t smem_raw[];
@@ -118,8 +119,8 @@ __global__ void __launch_bounds__(128) transpose_tma_kernel(const __grid_constan
   // diagonal thread -> block map: row group i (rows V*i .. V*i+V-1), 16-byte column chunk j
   const int lane = tid & 31, warp = tid >> 5;
   const int t8 = lane & 7;
-  const int bi = t8 + 8 * (warp & 1);
-  const int bj = (t8 + (lane >> 3) + 4 * (warp >> 1)) & 7;
+  const int bi = t8 + (RM_ == 2 ? 8 * (warp & 1) : 0);
+  const int bj = (t8 + (lane >> 3) + 4 * (RM_ == 2 ? (warp >> 1) : warp)) & 7;
   bool failed = false;
   for (long long i = 0; i < mine; ++i) {
     const int slot = (int)(i % SLOTS);
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(128) transpose_tma_kernel(const __grid_constan
       const int m0 = tm * Cfg::ROWS, n0 = tn * Cfg::COLS;
       uint8_t* o = out + (int)(i & 1) * STAGE;
       tma_store_2d(&tmD, o, m0, n0);
-      if (m0 + 8 * V < a.m) tma_store_2d(&tmD, o + Cfg::OUT_HALF, m0 + 8 * V, n0);
+      if (RM_ == 2 && m0 + 8 * V < a.m) tma_store_2d(&tmD, o + Cfg::OUT_HALF, m0 + 8 * V, n0);
       tma_store_commit();
     }
   }
@@ -170,20 +171,24 @@ __global__ void __launch_bounds__(128) transpose_tma_kernel(const __grid_constan
   }
 }
 
-template <int E>
+template <int E, int SLOTS_ = 2, int NB_ = 0, int RM_ = 1>
 static int launch_transpose_inst(moye_b200_ctx* h, const CUtensorMap& ts, const CUtensorMap& td, int64_t m, int64_t n,
                                  cudaStream_t stream) {
-  using Cfg = TransposeCfg<E>;
+  using Cfg = TransposeCfg<E, SLOTS_, NB_, RM_>;
   TransposeArgs a;
   a.m = (int)m;
   a.tiles_m = (int)((m + Cfg::ROWS - 1) / Cfg::ROWS);
   a.tiles = (long long)a.tiles_m * ((n + Cfg::COLS - 1) / Cfg::COLS);
   a.status = h->d_status;
-  auto kern = transpose_tma_kernel<E>;
+  auto kern = transpose_tma_kernel<E, SLOTS_, NB_, RM_>;
   if (int rc = configure_once(h, kern, Cfg::SMEM)) return rc;
-  const int per_sm = Cfg::SMEM > 110 * 1024 ? 1 : 2;
+  // Measured on 8192^2 (fp16 / fp32): 2 slots of 8 KB with 4 CTAs per SM reach 5.7 / 6.0 TB/s; deeper rings, larger
+  // stages or more CTAs per SM all lose 5-20 % (more requests in flight scatter over more DRAM pages).
+  int per_sm = 225 * 1024 / Cfg::SMEM;
+  if (per_sm > 4) per_sm = 4;
+  if (per_sm < 1) per_sm = 1;
   long long grid = a.tiles < (long long)h->num_sms * per_sm ? a.tiles : (long long)h->num_sms * per_sm;
-  kern<<<(int)grid, 128, Cfg::SMEM, stream>>>(ts, td, a);
+  kern<<<(int)grid, 64 * RM_, Cfg::SMEM, stream>>>(ts, td, a);
   MOYE_CUDA(cudaGetLastError());
   return MOYE_OK;
 }
@@ -202,8 +207,9 @@ int launch_transpose(moye_b200_ctx* h, void* dst, int64_t dst_pitch, const void*
     MOYE_FAIL(MOYE_ERR_MISALIGNED, "pitches must be multiples of 16 bytes");
   const int V = 16 / eb;
   const int nb = (8 / V) > 0 ? (8 / V) : 1;
+  const int rm = 1;  // rows of 8V x 8V sub-tiles per stage (TransposeCfg::RM)
   CUtensorMap ts, td;
-  if (int rc = make_tmap_2d(h, &ts, src, dtype, n, m, (uint64_t)src_pitch * eb, 8 * V, 16 * V, TMAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d(h, &ts, src, dtype, n, m, (uint64_t)src_pitch * eb, 8 * V, 8 * V * rm, TMAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d(h, &td, dst, dtype, m, n, (uint64_t)dst_pitch * eb, 8 * V, 8 * V * nb, TMAP_SWIZZLE_128B)) return rc;
   switch (eb) {
     case 1: return launch_transpose_inst<1>(h, ts, td, m, n, stream);
