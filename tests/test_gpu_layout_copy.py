@@ -135,6 +135,16 @@ def test_tiled_copy_matches_reference_copy_kernel(mb, ho, dev):
         mb.copyto_(narrow, mb.MoYeArray(dst, mb.make_layout((m, n))), mb.MoYeArray(src, mb.make_layout((m, n))))
 
 
+def test_tma_copy_tiles_of_growing_size_on_one_handle(mb, dev):
+    """The kernel's shared-memory limit is raised once per handle: it has to admit every legal tile, whatever tile the
+    first call used (a small first tile used to lock later, larger ones out)."""
+    for tile in ((64, 16), (128, 32), (128, 64), (256, 16)):
+        rc, src, dst = _roundtrip(mb, dev, 1024, 256, 2, tile=tile)
+        assert rc == 0, (tile, mb._lib.load().moye_b200_last_error())
+        mb.synchronize_status(dev)
+        assert torch.equal(src, dst), tile
+
+
 def _rand(dtype, numel, seed):
     g = torch.Generator(device="cpu").manual_seed(seed)
     if dtype.is_floating_point:
