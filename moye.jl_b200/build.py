@@ -14,7 +14,7 @@ OUT = os.path.join(HERE, "lib", "libmoye_b200.so")
 SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_skinny.cu", "copy_sm100.cu", "transpose_sm100.cu", "layout_sm100.cu"]
 HEADERS = ["common.h", "ptx.cuh", os.path.join("..", "..", "include", "moye_b200.h")]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
-         "-shared"]
+         "-shared", "--threads", "0"]  # the sources compile side by side: about 1.5 minutes from scratch on 8 cores
 
 
 def _stale():
