@@ -74,7 +74,7 @@ struct TransposeCfg {
   static constexpr int NB = NB_ ? NB_ : ((8 / V) > 0 ? (8 / V) : 1); // input boxes per stage: 8 KB stages (16 KB for 1-byte elements)
   static constexpr int ROWS = 8 * V * RM_;             // source rows (m) per stage
   static constexpr int COLS = 8 * V * NB;              // source columns (n) per stage
-  static constexpr int IN_BOX = ROWS * 128;            // bytes of one input box {8V, 16V}
+  static constexpr int IN_BOX = ROWS * 128;            // bytes of one input box {8V columns, 8V*RM rows}
   static constexpr int STAGE = IN_BOX * NB;
   static constexpr int OUT_HALF = STAGE / RM_;         // bytes of one output box {8V, 8V*NB}
   static constexpr int SLOTS = SLOTS_, LOOK = SLOTS_ - 1;
