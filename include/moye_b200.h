@@ -43,7 +43,8 @@ typedef enum {
   MOYE_ERR_CUDA = -6,
   MOYE_ERR_TIMEOUT = -7,   /* a bounded device-side wait ran out (see moye_b200_status) */
   MOYE_ERR_NO_DEVICE = -8,
-  MOYE_ERR_TOO_LARGE = -9
+  MOYE_ERR_TOO_LARGE = -9,
+  MOYE_ERR_NCCL = -10      /* NCCL is missing or one of its calls failed (multi-GPU entry points only) */
 } moye_status_t;
 
 /* Element types.  MoYe spells them Float32, Float16, BFloat16, Int8, UInt8, Int32; e4m3 is
@@ -93,7 +94,16 @@ enum {
   MOYE_EPI_ACT_MASK = 0xF,
   MOYE_EPI_BIAS_COL = 0x10,      /* bias[n], N floats: one value per column of D */
   MOYE_EPI_BIAS_ROW = 0x20,      /* bias[m], M floats: one value per row of D */
-  MOYE_EPI_BIAS_MASK = 0x30
+  MOYE_EPI_BIAS_MASK = 0x30,
+  /* Stream-K tail of the dense kernel on 256 x 512 tiles (path 0 or 4): when the last wave of tiles would leave
+   * CTA pairs idle, its tiles are cut along K into one run per pair and the pieces are added in K order (the
+   * result does not depend on timing; s8 stays exact).  The library decides from the shape; these bits overrule it. */
+  MOYE_GEMM_TAIL_OFF = 0x100,
+  MOYE_GEMM_TAIL_ON = 0x200,
+  /* Float32 operands.  Without this bit they are multiplied to Float32 accuracy (three tf32 tensor-core products of
+   * the operands' high and low parts, see moye_b200_gemm).  With it the caller accepts ONE tf32 product: operands are
+   * read with a 10-bit mantissa (the low 13 bits dropped), about 1e-3 relative, at three times the speed. */
+  MOYE_GEMM_ALLOW_TF32 = 0x400
 };
 
 /* Parameters of the tiled GEMM.  alpha/beta follow `axpby!` (reference
@@ -154,6 +164,13 @@ int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
  * reports MOYE_ERR_TIMEOUT with site code 901; the context stays usable.  No counterpart in the reference
  * (its kernels have no waits that can fail). */
 int moye_b200_selftest_bounded_wait(moye_handle_t h, void* stream);
+
+/* Second half of that integration test: overwrites the ticket areas of both stream-K scratch buffers of the handle
+ * (those that exist) with non-zero counts on `stream`, which is the state a kernel that gave up half-way would
+ * leave behind.  A following time-out report through moye_b200_status() must put them back to zero.  Never call
+ * this outside a test: the next stream-K product on the handle is wrong until moye_b200_status() has seen a
+ * time-out.  No counterpart in the reference. */
+int moye_b200_selftest_dirty_tickets(moye_handle_t h, void* stream);
 
 /* D = alpha*scale_a*scale_b * A.B^T + beta*C with A:(M,K), B:(N,K), C,D:(M,N).
  * Takes over the whole `matmul_kernel` of reference examples/gemm.jl:4-64 (the gemm!-based
@@ -217,9 +234,48 @@ int moye_b200_layout_eval(moye_handle_t h, const moye_layout_t* layout, int64_t 
  * them on one stream or with events.
  *
  * device_status: optional device int32 that receives a wait-site code if a bounded wait in
- * the kernel gives up (0 otherwise; the caller clears it); NULL keeps that word inside the array. */
+ * the kernel gives up (0 otherwise; the caller clears it); NULL keeps that word inside the array,
+ * where moye_b200_gemm_skinny_static_status() reads it. */
 int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                                  float alpha, int32_t* device_status, void* stream);
+
+/* Reads back what the most recent moye_b200_gemm_skinny_static() calls on this device recorded when they were
+ * given device_status == NULL: synchronises `stream`, copies the status word out of the static array (no
+ * allocation: a plain 4-byte cudaMemcpy) and returns MOYE_OK, or MOYE_ERR_TIMEOUT with the wait-site code in
+ * `site` (may be NULL).  The word is cleared by the next static GEMM call, so ask before launching another.
+ * No counterpart in the reference. */
+int moye_b200_gemm_skinny_static_status(void* stream, int32_t* site);
+
+/* Y = a*X + b*Y, elementwise over two rank-1 or rank-2 arrays of equal shape and element type (f32, f16, bf16) that
+ * are contiguous along the same mode: `axpby!` of reference src/algorithm/blas.jl:1-9 on global-memory arrays.  As
+ * there, Y is not read when b == 0.  Arithmetic as on the host: both products rounded to fp32, then added, one
+ * rounding to the element type.  X may be Y. */
+int moye_b200_axpby(moye_handle_t h, const moye_tensor_t* Y, const moye_tensor_t* X, float a, float b, void* stream);
+
+/* ---- several GPUs: one process (or thread) per GPU, each with its own handle ------------------------------------
+ * The reference has no multi-GPU code.  The hot path shards without any exchange: GEMM along M (rows of A and D, B
+ * replicated), weight-bound products along N (rows of W, columns of Y), copies along row blocks; every rank calls
+ * moye_b200_gemm / moye_b200_copy on its own block.  What needs the other GPUs is putting a result back together,
+ * or handing the replicated operand round; those two run on NCCL (looked up at run time as libnccl.so.2).
+ *
+ *   moye_b200_comm_unique_id   rank 0 makes a 128-byte id and hands it to the others by any host channel
+ *   moye_b200_comm_init        every rank, with its device current: joins (collective; blocks until all have)
+ *   moye_b200_allgather        every rank contributes its block of `full`; afterwards all hold all of it
+ *   moye_b200_bcast            `t` of rank `root` is copied into `t` of every rank
+ *   moye_b200_comm_destroy     leaves; moye_b200_destroy does not do this for you
+ *
+ * Blocks follow one rule everywhere: extent E along the split mode, cut into `world` blocks whose borders are
+ * multiples of `align` (units = ceil(E / align); rank r owns [units*r/world, units*(r+1)/world) * align, clipped
+ * to E).  `mode` is the split mode of `full` (0 or 1); it must be the OUTER mode in memory in both tensors, so
+ * that a block is one contiguous byte range (rows of a row-major matrix, columns of a column-major one);
+ * anything else is MOYE_ERR_UNSUPPORTED_LAYOUT.  `shard` may point into `full` (in place) or elsewhere.  Both
+ * collectives are asynchronous on `stream` like every other call. */
+int moye_b200_comm_unique_id(char* id128);
+int moye_b200_comm_init(moye_handle_t h, int32_t rank, int32_t world, const char* id128);
+int moye_b200_comm_destroy(moye_handle_t h);
+int moye_b200_allgather(moye_handle_t h, const moye_tensor_t* shard, const moye_tensor_t* full, int32_t mode,
+                        int64_t align, void* stream);
+int moye_b200_bcast(moye_handle_t h, const moye_tensor_t* t, int32_t root, void* stream);
 
 #ifdef __cplusplus
 }

@@ -19,7 +19,7 @@ COPY_AUTO, COPY_UNIVERSAL128, COPY_TMA, COPY_TRANSPOSE = 0, 1, 2, 3
 
 STATUS_NAMES = {
     0: "OK", -1: "INVALID_ARG", -2: "UNSUPPORTED_DTYPE", -3: "UNSUPPORTED_LAYOUT", -4: "UNSUPPORTED_SHAPE",
-    -5: "MISALIGNED", -6: "CUDA", -7: "TIMEOUT", -8: "NO_DEVICE", -9: "TOO_LARGE",
+    -5: "MISALIGNED", -6: "CUDA", -7: "TIMEOUT", -8: "NO_DEVICE", -9: "TOO_LARGE", -10: "NCCL",
 }
 
 
@@ -50,6 +50,8 @@ class GemmParams(ctypes.Structure):
 # fused-epilogue selectors of GemmParams.flags (MOYE_EPI_* in the header)
 EPI_ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "silu": 3}
 EPI_BIAS_COL, EPI_BIAS_ROW = 0x10, 0x20
+# kernel-choice bits of GemmParams.flags (MOYE_GEMM_* in the header)
+GEMM_TAIL_OFF, GEMM_TAIL_ON, GEMM_ALLOW_TF32 = 0x100, 0x200, 0x400
 
 
 class CopyParams(ctypes.Structure):
@@ -66,6 +68,7 @@ EXPORTS = {
     "moye_b200_last_error": (ctypes.c_char_p, []),
     "moye_b200_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]),
     "moye_b200_selftest_bounded_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "moye_b200_selftest_dirty_tickets": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "moye_b200_gemm": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
                                       ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.POINTER(GemmParams),
                                       ctypes.c_void_p]),
@@ -77,6 +80,15 @@ EXPORTS = {
     "moye_b200_gemm_skinny_static": (ctypes.c_int, [ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
                                                     ctypes.POINTER(Tensor), ctypes.c_float, ctypes.c_void_p,
                                                     ctypes.c_void_p]),
+    "moye_b200_gemm_skinny_static_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]),
+    "moye_b200_axpby": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.POINTER(Tensor), ctypes.c_float,
+                                       ctypes.c_float, ctypes.c_void_p]),
+    "moye_b200_comm_unique_id": (ctypes.c_int, [ctypes.c_char_p]),
+    "moye_b200_comm_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_char_p]),
+    "moye_b200_comm_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "moye_b200_allgather": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
+                                           ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]),
+    "moye_b200_bcast": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.c_int32, ctypes.c_void_p]),
     "moye_b200_layout_eval": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(FlatLayout), ctypes.c_int64,
                                              ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
 }

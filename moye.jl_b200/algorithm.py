@@ -21,7 +21,7 @@ from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
 from .layout import Layout, coalesce, size
 
 __all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
-           "gemm_skinny_static_", "plan_gemm", "plan_copy", "LaunchPlan"]
+           "gemm_skinny_static_", "gemm_skinny_static_status", "plan_gemm", "plan_copy", "LaunchPlan", "axpby_"]
 
 
 def current_stream_ptr(device=None):
@@ -146,15 +146,26 @@ def _epilogue(bias, activation, D, dev):
     return flags, ptr, bias
 
 
+def _choice_flags(allow_tf32, tail):
+    """The kernel-choice bits: `allow_tf32` lets Float32 operands run as ONE tf32 product (10-bit mantissas, about
+    1e-3 relative) instead of the three-product split that keeps Float32 accuracy; `tail` forces the stream-K tail
+    of the 256 x 512 kernel on (True) or off (False), None leaves the choice to the library."""
+    f = _lib.GEMM_ALLOW_TF32 if allow_tf32 else 0
+    if tail is not None:
+        f |= _lib.GEMM_TAIL_ON if tail else _lib.GEMM_TAIL_OFF
+    return f
+
+
 def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, stream=None, bias=None,
-          activation=None, split_k=0):
+          activation=None, split_k=0, allow_tf32=False, tail=None):
     """`gemm!([tiled_mma,] D, A, B, C)`: D = alpha*scale_a*scale_b * A.B^T + beta*C with
     A:(M,K), B:(N,K), C and D:(M,N) in global memory.  `gemm_(A, B, C)` is `gemm!(C, A, B, C)`
     like the reference's three-argument form (src/algorithm/blas.jl:11).  `bias` (float32, one
     value per column or per row of D) and `activation` ("relu", "gelu", "silu") are fused into the
     epilogue: D = act(alpha*... + beta*C + bias), in fp32 before the output conversion.  `path` picks the
     kernel (0: the library chooses; 1 single CTAs, 2 stream-K, 3 CTA pairs, 4 pairs on 256x512 tiles, 5 split-K on
-    clusters with `split_k` = 2, 4 or 8 CTAs per tile)."""
+    clusters with `split_k` = 2, 4 or 8 CTAs per tile).  Float32 operands are multiplied to Float32 accuracy unless
+    `allow_tf32=True` (see `_choice_flags`, also for `tail`)."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
         tiled_mma, args = args[0], args[1:]
@@ -178,6 +189,7 @@ def gemm_(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0
     lib, h = _lib.load(), _lib.handle(dev.index)
     st = stream if stream is not None else current_stream_ptr(dev)
     flags, bias_ptr, _ = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
+    flags |= _choice_flags(allow_tf32, tail)
     p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, split_k, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if (C is not None and beta != 0.0) else None
@@ -227,7 +239,7 @@ class LaunchPlan:
 
 
 def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, path=0, bias=None, activation=None,
-              split_k=0):
+              split_k=0, allow_tf32=False, tail=None):
     """`gemm_` with the argument marshalling done once; returns a `LaunchPlan`."""
     tiled_mma = None
     if args and isinstance(args[0], TiledMMA):
@@ -249,6 +261,7 @@ def plan_gemm(*args, alpha=1.0, beta=0.0, scale_a=1.0, scale_b=1.0, tile_n=0, pa
         tile_n = tile_n or op.shape_mnk[1]
     lib, h = _lib.load(), _lib.handle(dev.index)
     flags, bias_ptr, bias = _epilogue(bias, activation, D, dev) if (bias is not None or activation) else (0, None, None)
+    flags |= _choice_flags(allow_tf32, tail)
     p = _lib.GemmParams(alpha, beta, scale_a, scale_b, tile_n, split_k, path, flags, bias_ptr)
     tD, tA, tB = _tensor_arg(D, "D"), _tensor_arg(A, "A"), _tensor_arg(B, "B")
     tC = _tensor_arg(C, "C") if use_c else None
@@ -332,3 +345,36 @@ def gemm_skinny_static_(D, A, B, alpha=1.0, device_status=None, stream=None):
             ctypes.byref(_tensor_arg(D, "D")), ctypes.byref(_tensor_arg(A, "A")), ctypes.byref(_tensor_arg(B, "B")),
             ctypes.c_float(alpha), status_ptr, st))
     return D
+
+
+def gemm_skinny_static_status(device=None, stream=None):
+    """Synchronise `stream` and raise if a bounded wait inside a `gemm_skinny_static_` call that was given no
+    `device_status` ran out.  Allocates nothing, like the call it belongs to."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = stream if stream is not None else current_stream_ptr(device)
+    site = ctypes.c_int32(0)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().moye_b200_gemm_skinny_static_status(st, ctypes.byref(site)))
+
+
+def axpby_(a, X, b, Y, stream=None):
+    """`axpby!(a, X, b, Y)`: Y = a*X + b*Y elementwise on global-memory arrays (reference
+    src/algorithm/blas.jl:1-9); Y is not read when b == 0.  Returns Y."""
+    X, Y = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (X, Y))
+    dev = _need_gmem(Y, X)
+    lib, h = _lib.load(), _lib.handle(dev.index)
+    st = stream if stream is not None else current_stream_ptr(dev)
+
+    def arg(x, what):
+        l = coalesce(x.layout)
+        if not isinstance(l.shape, tuple):  # one mode after coalescing: a vector in memory order
+            if int(l.stride) != 1 and int(l.shape) != 1:
+                raise _lib.MoyeError(-3, f"axpby!: {what} is not contiguous")
+            return _lib.make_tensor(x.ptr, x.dtype, [int(l.shape)], [1])
+        return _tensor_arg(x, what)
+
+    tx, ty = arg(X, "X"), arg(Y, "Y")
+    if tx.rank != ty.rank:  # one of them coalesced to a vector, the other is pitched: use the rank-2 forms
+        tx, ty = _tensor_arg(X, "X"), _tensor_arg(Y, "Y")
+    _lib.check(lib.moye_b200_axpby(h, ctypes.byref(ty), ctypes.byref(tx), ctypes.c_float(a), ctypes.c_float(b), st))
+    return Y

@@ -122,17 +122,37 @@ int encode_tmap_2d_uncached(CUtensorMap* out, const void* ptr, int dtype, uint64
   return MOYE_OK;
 }
 
+// The skinny kernel's scratch is allocated once, at the size its widest instantiation needs, so that no launch
+// ever has to synchronise the device to free and re-allocate it.
 int ensure_workspace(moye_b200_ctx* h, size_t bytes) {
-  if (bytes <= h->workspace_bytes) return MOYE_OK;
   if (h->workspace) {
-    MOYE_CUDA(cudaDeviceSynchronize());
-    MOYE_CUDA(cudaFree(h->workspace));
-    h->workspace = nullptr;
-    h->workspace_bytes = 0;
+    if (bytes <= h->workspace_bytes) return MOYE_OK;
+    MOYE_FAIL(MOYE_ERR_TOO_LARGE, "the stream-K scratch holds %zu bytes, %zu were asked for", h->workspace_bytes, bytes);
   }
   size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-  MOYE_CUDA(cudaMalloc(&h->workspace, want));
+  void* p = nullptr;
+  MOYE_CUDA(cudaMalloc(&p, want));
+  cudaError_t e = cudaMemset(p, 0, kSkinnyTicketBytes);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    MOYE_FAIL(MOYE_ERR_CUDA, "clearing the stream-K tickets failed: %s", cudaGetErrorString(e));
+  }
   h->workspace_bytes = want;
+  h->workspace = p;
+  return MOYE_OK;
+}
+
+int order_scratch_use(moye_b200_ctx* h, ScratchOrder* o, cudaStream_t stream) {
+  (void)h;
+  if (!o->done) MOYE_CUDA(cudaEventCreateWithFlags(&o->done, cudaEventDisableTiming));
+  if (o->used && o->last != stream) MOYE_CUDA(cudaStreamWaitEvent(stream, o->done, 0));
+  return MOYE_OK;
+}
+
+int scratch_used(ScratchOrder* o, cudaStream_t stream) {
+  MOYE_CUDA(cudaEventRecord(o->done, stream));
+  o->last = stream;
+  o->used = true;
   return MOYE_OK;
 }
 
@@ -205,6 +225,11 @@ int moye_b200_destroy(moye_handle_t h) {
   cudaDeviceSynchronize();
   if (h->d_status) cudaFree(h->d_status);
   if (h->workspace) cudaFree(h->workspace);
+  if (h->tail_ws) cudaFree(h->tail_ws);
+  if (h->split_ws) cudaFree(h->split_ws);
+  if (h->split_order.done) cudaEventDestroy(h->split_order.done);
+  if (h->sk_order.done) cudaEventDestroy(h->sk_order.done);
+  if (h->tail_order.done) cudaEventDestroy(h->tail_order.done);
   delete h;
   return MOYE_OK;
 }
@@ -216,7 +241,13 @@ int moye_b200_status(moye_handle_t h, void* stream, int32_t* site) {
   MOYE_CUDA(cudaMemcpy(&v, h->d_status, sizeof(int), cudaMemcpyDeviceToHost));
   if (site) *site = v;
   if (v != 0) {
+    // A kernel that gave up may have left stream-K tickets half counted: whoever would have restored them never
+    // arrived.  Nothing of this handle is running any more on `stream`; wait for its other streams too, then put
+    // both ticket areas back to zero so that the next product starts clean.
+    MOYE_CUDA(cudaDeviceSynchronize());
     MOYE_CUDA(cudaMemset(h->d_status, 0, sizeof(int)));
+    if (h->workspace) MOYE_CUDA(cudaMemset(h->workspace, 0, kSkinnyTicketBytes));
+    if (h->tail_ws) MOYE_CUDA(cudaMemset(h->tail_ws, 0, kTailTicketBytes));
     MOYE_FAIL(MOYE_ERR_TIMEOUT, "a bounded device-side wait ran out (site code %d)", v);
   }
   return MOYE_OK;
@@ -226,6 +257,14 @@ int moye_b200_selftest_bounded_wait(moye_handle_t h, void* stream) {
   if (int rc = check_handle(h)) return rc;
   moye::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(h->d_status);
   MOYE_CUDA(cudaGetLastError());
+  return MOYE_OK;
+}
+
+int moye_b200_selftest_dirty_tickets(moye_handle_t h, void* stream) {
+  if (int rc = check_handle(h)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (h->workspace) MOYE_CUDA(cudaMemsetAsync(h->workspace, 0x01, kSkinnyTicketBytes, s));
+  if (h->tail_ws) MOYE_CUDA(cudaMemsetAsync(h->tail_ws, 0x01, kTailTicketBytes, s));
   return MOYE_OK;
 }
 
@@ -241,6 +280,12 @@ int moye_b200_copy(moye_handle_t h, const moye_tensor_t* dst, const moye_tensor_
   if (int rc = check_handle(h)) return rc;
   if (!dst || !src) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "dst and src must be non-null");
   return launch_copy(h, dst, src, params, static_cast<cudaStream_t>(stream));
+}
+
+int moye_b200_axpby(moye_handle_t h, const moye_tensor_t* Y, const moye_tensor_t* X, float a, float b, void* stream) {
+  if (int rc = check_handle(h)) return rc;
+  if (!Y || !X) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "Y and X must be non-null");
+  return launch_axpby(h, Y, X, a, b, static_cast<cudaStream_t>(stream));
 }
 
 int moye_b200_layout_copy(moye_handle_t h, void* dst, const moye_layout_t* dl, const void* src,

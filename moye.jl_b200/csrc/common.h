@@ -66,14 +66,28 @@ struct TmapKeyHash {
 
 }  // namespace moye
 
+// Orders the launches that share one scratch buffer of a handle when they come on different streams.
+struct ScratchOrder {
+  cudaEvent_t done = nullptr;       // recorded after the last launch that used the buffer
+  cudaStream_t last = nullptr;
+  bool used = false;
+};
+
 // The handle.  One per (host thread, device).
 struct moye_b200_ctx {
   int device = -1;
   int num_sms = 0;
   int smem_optin = 0;
   int* d_status = nullptr;          // device status word (0 = OK, else wait-site code)
-  void* workspace = nullptr;        // stream-K partial sums
+  void* workspace = nullptr;        // stream-K scratch of the skinny kernel: tickets, then partial sums
   size_t workspace_bytes = 0;
+  void* tail_ws = nullptr;          // stream-K tail of the dense 256 x 512 kernel: tickets, then partial accumulators
+  size_t tail_ws_bytes = 0;
+  void* split_ws = nullptr;         // lo(A), lo(B) of the Float32 GEMM's three-product split
+  size_t split_ws_bytes = 0;
+  ScratchOrder sk_order, tail_order, split_order;
+  void* comm = nullptr;             // ncclComm_t of this rank (comm_nccl.cu), null until moye_b200_comm_init
+  int comm_rank = 0, comm_world = 0;
   std::mutex mu;
   std::unordered_map<moye::TmapKey, CUtensorMap, moye::TmapKeyHash> tmaps;
   std::unordered_set<const void*> configured;   // kernels whose dynamic-smem limit is already raised
@@ -111,6 +125,14 @@ inline int configure_once(moye_b200_ctx* h, K kernel, int smem_bytes) {
 
 // Grows the handle-owned workspace to at least `bytes` (never shrinks).
 int ensure_workspace(moye_b200_ctx* h, size_t bytes);
+// Ticket areas at the front of both stream-K scratch buffers (zero whenever no kernel is running).
+constexpr size_t kSkinnyTicketBytes = 64 * 1024;
+constexpr size_t kTailTicketBytes = 64 * 1024;
+int ensure_tail_workspace(moye_b200_ctx* h);
+// Before a launch that uses a shared scratch buffer: if the previous user ran on another stream, make `stream`
+// wait for it.  After the launch: remember it.  Launches on one stream pay an event record and nothing else.
+int order_scratch_use(moye_b200_ctx* h, ScratchOrder* o, cudaStream_t stream);
+int scratch_used(ScratchOrder* o, cudaStream_t stream);
 
 int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                 const moye_tensor_t* C, const moye_gemm_params_t* p, cudaStream_t stream);
@@ -118,6 +140,7 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst, const moye_tensor_t*
                 cudaStream_t stream);
 int launch_transpose(moye_b200_ctx* h, void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int dtype,
                      int64_t m, int64_t n, cudaStream_t stream);
+int launch_axpby(moye_b200_ctx* h, const moye_tensor_t* Y, const moye_tensor_t* X, float a, float b, cudaStream_t stream);
 int launch_layout_copy(moye_b200_ctx* h, void* dst, const moye_layout_t* dl, const void* src,
                        const moye_layout_t* sl, int elem_bytes, cudaStream_t stream);
 int launch_layout_eval(moye_b200_ctx* h, const moye_layout_t* l, int64_t first, int64_t n, int64_t* out,

@@ -398,22 +398,22 @@ static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUt
   // costs more than the extra CTAs bring (4096 x 512 weights: 10.6 us against 16 with 148 CTAs)
   long long grid = h->num_sms;
   if (grid > a.units / kMinRun) grid = a.units / kMinRun > 0 ? a.units / kMinRun : 1;
-  // workspace: a fixed ticket area (zero at rest: the kernel restores it) then the partial slots
-  constexpr size_t kTicketBytes = 64 * 1024;
-  if ((size_t)a.n_tiles * sizeof(int) > kTicketBytes)
+  // workspace: a fixed ticket area (zero at rest: the kernel restores it, moye_b200_status() clears it after a
+  // time-out) then the partial slots.  It is allocated once, sized for the widest X tile, so no launch ever frees
+  // or re-allocates it.
+  if ((size_t)a.n_tiles * sizeof(int) > kSkinnyTicketBytes)
     MOYE_FAIL(MOYE_ERR_TOO_LARGE, "N = %d exceeds the %zu row-blocks the ticket area holds", a.N,
-              kTicketBytes / sizeof(int));
-  const size_t part_bytes = (size_t)h->num_sms * 2 * NX * 128 * sizeof(float);
-  const size_t need = kTicketBytes + part_bytes;
-  if (need > h->workspace_bytes) {
-    if (int rc = ensure_workspace(h, need)) return rc;
-    MOYE_CUDA(cudaMemsetAsync(h->workspace, 0, kTicketBytes, stream));
+              kSkinnyTicketBytes / sizeof(int));
+  if (!h->workspace) {
+    if (int rc = ensure_workspace(h, kSkinnyTicketBytes + (size_t)h->num_sms * 2 * 128 * 128 * sizeof(float))) return rc;
   }
   a.tickets = reinterpret_cast<int*>(h->workspace);
-  a.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->workspace) + kTicketBytes);
+  a.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->workspace) + kSkinnyTicketBytes);
+  // every stream-K launch of a handle shares that scratch: a launch on another stream than the last one waits for it
+  if (int rc = order_scratch_use(h, &h->sk_order, stream)) return rc;
   kern<<<(int)grid, 192, SMEM, stream>>>(tw, tx, a);
   MOYE_CUDA(cudaGetLastError());
-  return MOYE_OK;
+  return scratch_used(&h->sk_order, stream);
 }
 
 template <int NX>
@@ -563,7 +563,8 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   if (M > kStaticMaxNx)
     MOYE_FAIL(MOYE_ERR_TOO_LARGE, "M = %lld exceeds the %d rows the static scratch is sized for", (long long)M,
               kStaticMaxNx);
-  if (K > INT32_MAX / 2 || N > (int64_t)kStaticMaxRowBlocks * 128)
+  if (K > INT32_MAX / 2) MOYE_FAIL(MOYE_ERR_TOO_LARGE, "K = %lld is too large", (long long)K);
+  if (N > (int64_t)kStaticMaxRowBlocks * 128)
     MOYE_FAIL(MOYE_ERR_TOO_LARGE, "N = %lld exceeds the %lld rows of W the static scratch is sized for (%d row blocks)",
               (long long)N, (long long)kStaticMaxRowBlocks * 128, kStaticMaxRowBlocks);
   StaticSetup* su = nullptr;
@@ -571,7 +572,7 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   if (su->num_sms > kStaticMaxSms)
     MOYE_FAIL(MOYE_ERR_TOO_LARGE, "%d SMs exceed the %d the static scratch is sized for", su->num_sms, kStaticMaxSms);
 
-  const int nx = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const int nx = M <= 16 ? 16 : 32;  // M <= kStaticMaxNx was checked above
   CUtensorMap tw, tx;
   if (int rc = encode_tmap_2d_uncached(&tw, B->ptr, B->dtype, K, N, (uint64_t)B->stride[0] * 2, 64, 128, true)) return rc;
   if (int rc = encode_tmap_2d_uncached(&tx, A->ptr, A->dtype, K, M, (uint64_t)A->stride[0] * 2, 64, nx, true)) return rc;
@@ -608,5 +609,17 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
     else launch_skinny_static<__nv_bfloat16, 32>(tw, tx, a, (int)grid, stream);
   }
   MOYE_CUDA(cudaGetLastError());
+  return MOYE_OK;
+}
+
+extern "C" int moye_b200_gemm_skinny_static_status(void* stream_, int32_t* site) {
+  using namespace moye;
+  StaticSetup* su = nullptr;
+  if (int rc = static_setup_for_current_device(&su)) return rc;
+  MOYE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)));
+  int v = 0;
+  MOYE_CUDA(cudaMemcpy(&v, su->base, sizeof(int), cudaMemcpyDeviceToHost));
+  if (site) *site = v;
+  if (v != 0) MOYE_FAIL(MOYE_ERR_TIMEOUT, "a bounded wait inside the static skinny GEMM ran out (site code %d)", v);
   return MOYE_OK;
 }

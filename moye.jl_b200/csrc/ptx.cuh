@@ -104,6 +104,17 @@ __device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* m, const vo
                "r"(smem_u32(smem_src)), "r"(x), "r"(y), "l"(policy)
                : "memory");
 }
+// 2-D tiled reduction shared -> global: every element of the box is ADDED to the element in global memory (the
+// element type is the tensor map's; the add happens at the memory side, nothing is read back).  Completion is
+// tracked like a store.  Parts of the box outside the tensor are clipped.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// Orders this thread's earlier and later accesses across the generic and the async proxy, all state spaces.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

@@ -216,6 +216,19 @@ def fused_epilogue(acc, alpha=1.0, beta=0.0, C=None, bias=None, bias_mode=None, 
     return x.astype(np.float32)
 
 
+def axpby(a, x, b, y):
+    """`axpby!(a, X, b, Y)` of reference src/algorithm/blas.jl:1-9 over two equally shaped float32 arrays (16-bit
+    element types are widened by the caller, exactly): every element `a*x` when b == 0 (Y is not read), else
+    `a*x + b*y` with both products rounded to Float32 before the add -- Julia does not contract the expression.
+    Returns float32; the caller rounds to the element type (round to nearest even) like the store does."""
+    a32, b32 = np.float32(a), np.float32(b)
+    x = np.asarray(x, dtype=np.float32)
+    ax = a32 * x
+    if b32 == 0:
+        return ax
+    return ax + b32 * np.asarray(y, dtype=np.float32)
+
+
 def tf32_trunc(x):
     """Float32 values as the tf32 tensor-core kind reads them: sign, 8 exponent bits and the top 10 mantissa
     bits; the low 13 bits are dropped without rounding (measured on sm_100a: truncation reproduces the device

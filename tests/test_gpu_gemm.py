@@ -11,7 +11,13 @@ import torch
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 NTHREADS = max(1, min(64, os.cpu_count() or 1))
-TOL = {"f16": 1e-2, "bf16": 1e-2, "e4m3": 3e-2, "f32": 1e-2}  # f32 runs on the tf32 kind (10-bit mantissa)
+TOL = {"f16": 1e-2, "bf16": 1e-2, "e4m3": 3e-2, "f32": 1e-2}  # "f32" here: ONE tf32 product (allow_tf32), 10-bit mantissas
+TOL_F32X3 = 1e-5  # Float32 operands without allow_tf32: the three-product split, against the fp32 host gemm! on raw operands
+
+
+def kw_of(kind):
+    """Float32 operands are compared with the oracle on tf32-truncated operands: ask for the single tf32 product."""
+    return {"allow_tf32": True} if kind == "f32" else {}
 
 
 def dev_bits(bits, dtype, shape, dev):
@@ -78,7 +84,7 @@ def test_small_goldens_all_dtypes(mb, ho, dev):
 
 @pytest.mark.parametrize("kind", ["f16", "bf16", "s8", "e4m3", "f32"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 1024), (384, 520, 1008), (1, 8, 16), (130, 72, 4096),
-                                   (1024, 1024, 512)])
+                                   (1024, 1024, 512), (520, 1040, 2000)])
 def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
     """Whole C against the oracle, ragged edges included, for every tile width and both
     output majors."""
@@ -91,15 +97,20 @@ def test_gemm_full_oracle(mb, ho, dev, kind, M, N, K):
     for m_major in (False, True):
         if m_major and (M * torch.empty(0, dtype=out_dtype).element_size()) % 16:
             continue
-        for path, tile_n in ((1, 0), (1, 64), (1, 128), (1, 256), (3, 128), (3, 256), (4, 0), (0, 0)):
+        # 1 single CTAs, 3 CTA pairs, 4 pairs on 256x512 tiles (with and without the stream-K tail), 5 split-K on
+        # clusters of 2 / 4 / 8 CTAs (K = 64 or 16 gives cluster ranks without any K block), 0 the library's choice
+        for path, tile_n, extra in ((1, 0, {}), (1, 64, {}), (1, 128, {}), (1, 256, {}), (3, 128, {}), (3, 256, {}),
+                                    (4, 0, {"tail": False}), (4, 0, {"tail": True}), (0, 0, {}),
+                                    (5, 0, {"split_k": 2}), (5, 128, {"split_k": 4}), (5, 256, {"split_k": 8}),
+                                    (5, 0, {})):
             C = out_tensor(M, N, out_dtype, dev, m_major)
-            mb.matmul(A, B, C, tile_n=tile_n, path=path)  # 1 single CTAs, 3 CTA pairs, 4 pairs on 256x512 tiles, 0 auto
+            mb.matmul(A, B, C, tile_n=tile_n, path=path, **extra, **kw_of(kind))
             mb.synchronize_status(dev)
             got = C.float().cpu().numpy() if kind != "s8" else C.cpu().numpy()
             if kind == "s8":
-                assert np.array_equal(got, ref), (m_major, path, tile_n)
+                assert np.array_equal(got, ref), (m_major, path, tile_n, extra)
             else:
-                assert ho.max_rel_err(got, ref) <= TOL[kind], (m_major, path, tile_n)
+                assert ho.max_rel_err(got, ref) <= TOL[kind], (m_major, path, tile_n, extra)
 
 
 def col_major(t):
@@ -121,7 +132,7 @@ def test_gemm_mn_major_operands(mb, ho, dev, kind, M, N, K):
         for path in (1, 3, 4):
             for m_major in (False, True):
                 C = out_tensor(M, N, torch.int32 if kind == "s8" else torch.float32, dev, m_major)
-                mb.matmul(Ax, Bx, C, path=path)
+                mb.matmul(Ax, Bx, C, path=path, **kw_of(kind), **({"tail": True} if path == 4 else {}))
                 mb.synchronize_status(dev)
                 if kind == "s8":
                     assert np.array_equal(C.cpu().numpy(), ref), (a_mn, b_mn, path, m_major)
@@ -158,7 +169,7 @@ def test_examples_gemm_jl_float32(mb, ho, dev):
     A = mb.MoYeArray(torch.from_numpy(a).to(dev), mb.make_layout((M, K)))
     B = mb.MoYeArray(torch.from_numpy(b).to(dev), mb.make_layout((N, K)))
     Cbuf = torch.zeros(M * N, device=dev)
-    mb.matmul(A, B, mb.MoYeArray(Cbuf, mb.make_layout((M, N))))
+    mb.matmul(A, B, mb.MoYeArray(Cbuf, mb.make_layout((M, N))), allow_tf32=True)
     mb.synchronize_status(dev)
     got = Cbuf.cpu().numpy()
     want = ho.gemm_f32(ho.tf32_trunc(a), (1, M), ho.tf32_trunc(b), (1, N), M, N, K)   # host gemm!, column-major, tf32 view
@@ -166,6 +177,11 @@ def test_examples_gemm_jl_float32(mb, ho, dev):
     raw = ho.gemm_f32(a, (1, M), b, (1, N), M, N, K)                                    # host gemm! on the raw Float32
     bound = ho.gemm_f32(np.abs(a), (1, M), np.abs(b), (1, N), M, N, K)
     assert np.all(np.abs(got - raw) <= 2.0 ** -9 * bound)
+    # the default for Float32 operands: three tf32 products of high and low parts, Float32 accuracy
+    Cbuf.zero_()
+    mb.matmul(A, B, mb.MoYeArray(Cbuf, mb.make_layout((M, N))))
+    mb.synchronize_status(dev)
+    assert ho.max_rel_err(Cbuf.cpu().numpy(), raw) <= TOL_F32X3
 
 
 def test_config1_fp32_against_committed_golden(mb, ho, dev):
@@ -179,13 +195,18 @@ def test_config1_fp32_against_committed_golden(mb, ho, dev):
     B = mb.MoYeArray(torch.from_numpy(b).to(dev), mb.make_layout((N, K)))
     for path in (1, 3, 0):
         cbuf = torch.zeros(M * N, device=dev)
-        mb.matmul(A, B, mb.MoYeArray(cbuf, mb.make_layout((M, N))), path=path)
+        mb.matmul(A, B, mb.MoYeArray(cbuf, mb.make_layout((M, N))), path=path, allow_tf32=True)
         mb.synchronize_status(dev)
         got = cbuf.cpu().numpy().reshape(N, M).T
         bound = ho.gemm_f32(np.abs(a), (1, M), np.abs(b), (1, N), M, N, K).reshape(N, M).T
         assert np.all(np.abs(got - gold) <= 2.0 ** -9 * bound), path
         want = ho.gemm_f32(ho.tf32_trunc(a), (1, M), ho.tf32_trunc(b), (1, N), M, N, K).reshape(N, M).T
         assert ho.max_rel_err(got, want) <= TOL["f32"], path
+        # Float32 accuracy (the default): the committed golden itself, to 1e-5 of the test metric
+        cbuf.zero_()
+        mb.matmul(A, B, mb.MoYeArray(cbuf, mb.make_layout((M, N))), path=path)
+        mb.synchronize_status(dev)
+        assert ho.max_rel_err(cbuf.cpu().numpy().reshape(N, M).T, gold) <= TOL_F32X3, path
 
 
 def test_alpha_beta_and_low_precision_outputs(mb, ho, dev):
@@ -245,7 +266,8 @@ def test_fused_bias_activation_epilogue(mb, ho, dev, kind, out):
         D = out_tensor(M, N, out, dev, m_major)
         tb = None if which is None else ((Bc if which == "col" else Br) * alpha).contiguous()
         mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(Cin) if beta else None, alpha=alpha,
-                 beta=beta, tile_n=tile_n, path=path, bias=tb, activation=act)
+                 beta=beta, tile_n=tile_n, path=path, bias=tb, activation=act, **kw_of(kind),
+                 **({"tail": True} if path == 4 else {}))
         mb.synchronize_status(dev)
         want = ho.fused_epilogue(acc, alpha, beta, Cin.float().cpu().numpy(), bias, which, act)
         err = ho.max_rel_err(D.float().cpu().numpy(), want)
@@ -327,11 +349,12 @@ def sampled_check(mb, ho, dev, kind, M, N, K, seeds, out_dtype, tol, nsample=128
     return A, B, C
 
 
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
 @pytest.mark.parametrize("n", [4096, 8192])
-def test_config3_fp16_dense(mb, ho, dev, n):
-    """fp16 x fp16 -> fp32, M=N=K=n, U[-1,1) seeds 3/4: 128 full rows and 128 full columns
+def test_config3_fp16_dense(mb, ho, dev, n, kind):
+    """fp16 x fp16 -> fp32 (and bf16), M=N=K=n, seeds 3/4: 128 full rows and 128 full columns
     against the oracle, and the whole matrix against a second, independent device product."""
-    A, B, C = sampled_check(mb, ho, dev, "f16", n, n, n, (3, 4), torch.float32, 1e-2)
+    A, B, C = sampled_check(mb, ho, dev, kind, n, n, n, (3, 4), torch.float32, 1e-2)
     other = torch.matmul(A.float(), B.float().t())  # secondary cross-check only (fp32 cuBLAS)
     err = ((C - other).abs().max() / other.abs().max()).item()
     assert err <= 1e-3
@@ -429,8 +452,12 @@ def test_gemm_argument_errors(mb, dev):
     assert call(B=T(buf.data_ptr(), F16, [128, 32], [32, 1])) == -4                   # K mismatch
     assert call(B=T(buf.data_ptr(), mb._lib.BF16, [128, 64], [64, 1])) == -2          # mixed operand types
     assert call(D=T(out.data_ptr(), mb._lib.S32, [128, 128], [128, 1])) == -2         # f16 -> s32 unsupported
-    assert call(A=T(buf.data_ptr(), F32, [128, 32], [32, 1]), B=T(buf.data_ptr(), F32, [128, 32], [32, 1])) == 0   # f32 -> tf32 kind
-    assert call(A=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1]), B=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1])) == -2
+    assert call(A=T(buf.data_ptr(), F32, [128, 32], [32, 1]), B=T(buf.data_ptr(), F32, [128, 32], [32, 1])) == 0   # f32: three tf32 products
+    assert call(A=T(buf.data_ptr(), F32, [128, 32], [32, 1]), B=T(buf.data_ptr(), F32, [128, 32], [32, 1]),
+                p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 0, mb._lib.GEMM_ALLOW_TF32)) == 0               # f32: one tf32 product
+    assert call(A=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1]), B=T(buf.data_ptr(), mb._lib.U8, [128, 64], [64, 1])) == -2  # u8 -> f32
+    assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 4, mb._lib.GEMM_TAIL_ON | mb._lib.GEMM_TAIL_OFF)) == -1   # contradictory bits
+    assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 0, 0, 0, 0x1000)) == -1                                   # unknown bit
     assert call(p=mb._lib.GemmParams(1.0, 1.0, 1.0, 1.0, 0, 0, 0, 0)) == -1           # beta without C
     assert call(p=mb._lib.GemmParams(1.0, 0.0, 1.0, 1.0, 96, 0, 0, 0)) == -1          # bad tile_n
     big = T(buf.data_ptr(), F16, [256, 64], [64, 1])
@@ -507,3 +534,127 @@ def test_bounded_wait_gives_up_and_the_context_survives(mb, ho, dev):
     mb.synchronize_status(dev)
     ref = ho.gemm_samples(a, b, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
     assert ho.max_rel_err(C.cpu().numpy(), ref) <= 1e-2
+
+
+def test_stale_stream_k_tickets_are_cleared_after_a_timeout(mb, ho, dev):
+    """A kernel that gives up can leave stream-K tickets half counted.  Provoked without a fault: the self-test
+    kernel runs out of patience (the only kernel that ever should), the host scribbles non-zero tickets into both
+    scratch areas as a broken kernel would have, `moye_b200_status` reports the time-out -- and must leave both
+    ticket areas zero, so that the next stream-K products on that handle are right."""
+    lib, h = mb._lib.load(), mb._lib.handle(dev.index)
+    st = mb.current_stream_ptr(dev)
+    M, N, K = 16, 2048, 2048
+    x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
+    ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    Y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    mb.matmul(X, W, Y, path=2)                      # makes sure the skinny scratch exists
+    Md, Nd, Kd = 512, 1024, 1024
+    a, b, A, B, dtd = operands(ho, "f16", Md, Nd, Kd, dev, (3, 4))
+    refd = ho.gemm_samples(a, b, dtd, Md, Nd, Kd, np.arange(Md, dtype=np.int32), threads=NTHREADS)
+    C = torch.zeros(Md, Nd, device=dev)
+    mb.matmul(A, B, C, path=4, tail=True)           # ... and the dense tail's
+    mb.synchronize_status(dev)
+    assert lib.moye_b200_selftest_dirty_tickets(h, st) == 0
+    assert lib.moye_b200_selftest_bounded_wait(h, st) == 0
+    site = ctypes.c_int32(0)
+    assert lib.moye_b200_status(h, st, ctypes.byref(site)) == -7 and site.value == 901
+    Y.zero_()
+    mb.matmul(X, W, Y, path=2)
+    C.zero_()
+    mb.matmul(A, B, C, path=4, tail=True)
+    mb.synchronize_status(dev)
+    assert ho.max_rel_err(Y.float().cpu().numpy(), ref) <= 1e-2
+    assert ho.max_rel_err(C.cpu().numpy(), refd) <= 1e-2
+
+
+def test_stream_k_on_two_streams_of_one_handle(mb, ho, dev):
+    """Stream-K launches of one handle share its scratch.  Alternating products on two streams must not disturb
+    each other: the library orders them with an event."""
+    M, N, K = 16, 4096, 4096
+    x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
+    x2, w2, X2, W2, _ = operands(ho, "bf16", M, N, K, dev, (11, 12))
+    ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    ref2 = ho.gemm_samples(x2, w2, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    torch.cuda.synchronize()
+    Y1 = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(8)]
+    Y2 = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(8)]
+    for i in range(8):
+        mb.matmul(X, W, Y1[i], path=2, stream=ctypes.c_void_p(s1.cuda_stream))
+        mb.matmul(X2, W2, Y2[i], path=2, stream=ctypes.c_void_p(s2.cuda_stream))
+    torch.cuda.synchronize()
+    mb.synchronize_status(dev)
+    for i in range(8):
+        assert ho.max_rel_err(Y1[i].float().cpu().numpy(), ref) <= 1e-2, i
+        assert ho.max_rel_err(Y2[i].float().cpu().numpy(), ref2) <= 1e-2, i
+        assert torch.equal(Y1[i], Y1[0]) and torch.equal(Y2[i], Y2[0])
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (1024, 8192, 8192), (300, 520, 1000), (2304, 1536, 768)])
+def test_stream_k_tail_equals_whole_tiles(mb, ho, dev, M, N, K):
+    """The stream-K tail only changes who computes which K blocks: s8 results are identical to the whole-tile
+    schedule, fp16 results agree with the oracle and do not depend on timing (two runs are bit-equal)."""
+    a8, b8, A8, B8, _ = operands(ho, "s8", M, N, K, dev, (5, 6))
+    outs = []
+    for tail in (False, True, True):
+        C = torch.zeros(M, N, dtype=torch.int32, device=dev)
+        mb.matmul(A8, B8, C, path=4, tail=tail)
+        mb.synchronize_status(dev)
+        outs.append(C)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    rows = np.arange(0, M, max(1, M // 64), dtype=np.int32)
+    assert np.array_equal(outs[1].cpu().numpy()[rows], ho.gemm_samples(a8, b8, ho.S8, M, N, K, rows, threads=NTHREADS))
+    del outs, A8, B8
+    a, b, A, B, dt = operands(ho, "f16", M, N, K, dev, (3, 4))
+    ref = ho.gemm_samples(a, b, dt, M, N, K, rows, threads=NTHREADS)
+    got = []
+    for m_major in (False, True, False):
+        C = out_tensor(M, N, torch.float32, dev, m_major)
+        mb.matmul(A, B, C, path=4, tail=True)
+        mb.synchronize_status(dev)
+        assert ho.max_rel_err(C.cpu().numpy()[rows], ref) <= 1e-2
+        got.append(C.contiguous())
+    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2])
+
+
+@pytest.mark.parametrize("ka,kb", [("u8", "u8"), ("u8", "s8"), ("s8", "u8")])
+def test_unsigned_8bit_operands(mb, ho, dev, ka, kb):
+    """UInt8 operands, also mixed with Int8 (the reference's S32U8U8S32 / S32U8S8S32 / S32S8U8S32 ops,
+    src/arch/mma/make_mma_ops.jl:143-160): bit-exact against the host gemm! in Int32 on widened inputs."""
+    M, N, K = 384, 520, 1008
+    rs = ho.rng(71)
+    a = rs.integers(0, 256, M * K, dtype=np.int64) if ka == "u8" else rs.integers(-128, 128, M * K, dtype=np.int64)
+    b = rs.integers(0, 256, N * K, dtype=np.int64) if kb == "u8" else rs.integers(-128, 128, N * K, dtype=np.int64)
+    ref = ho.gemm_s32(a.astype(np.int32), (K, 1), b.astype(np.int32), (K, 1), M, N, K, c_strides=(N, 1)).reshape(M, N)
+    A = torch.from_numpy(a.astype(np.uint8 if ka == "u8" else np.int8)).to(dev).view(M, K)
+    B = torch.from_numpy(b.astype(np.uint8 if kb == "u8" else np.int8)).to(dev).view(N, K)
+    for path, extra in ((1, {}), (3, {}), (4, {"tail": True}), (5, {}), (0, {})):
+        C = torch.zeros(M, N, dtype=torch.int32, device=dev)
+        mb.matmul(A, B, C, path=path, **extra)
+        mb.synchronize_status(dev)
+        assert np.array_equal(C.cpu().numpy(), ref), (path, extra)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (384, 520, 1008), (2048, 2048, 512)])
+def test_float32_three_product_split(mb, ho, dev, M, N, K):
+    """Float32 operands without allow_tf32: hi/lo split on the tf32 tensor-core kind, to 1e-5 of the test metric
+    of the fp32 host gemm! on the raw operands (the arithmetic the reference's Float32 example runs,
+    examples/gemm.jl:91-96), row- and column-major, with alpha / beta and a fused bias."""
+    a, b = ho.uniform_pm1(3, (M * K,)), ho.uniform_pm1(4, (N * K,))
+    raw = ho.gemm_f32(a, (K, 1), b, (K, 1), M, N, K, c_strides=(N, 1)).reshape(M, N)
+    A, B = torch.from_numpy(a).to(dev).view(M, K), torch.from_numpy(b).to(dev).view(N, K)
+    for a_mn, b_mn, m_major in ((False, False, False), (True, True, True), (True, False, False)):
+        if (a_mn and M % 4) or (b_mn and N % 4) or (m_major and M % 4):
+            continue
+        C = out_tensor(M, N, torch.float32, dev, m_major)
+        mb.matmul(col_major(A) if a_mn else A, col_major(B) if b_mn else B, C)
+        mb.synchronize_status(dev)
+        assert ho.max_rel_err(C.cpu().numpy(), raw) <= TOL_F32X3, (a_mn, b_mn, m_major)
+    cin = ho.rng(5).standard_normal((M, N)).astype(np.float32) * np.float32(K ** 0.5)
+    bias = ho.rng(6).standard_normal(N).astype(np.float32)
+    D = torch.zeros(M, N, device=dev)
+    mb.gemm_(mb.MoYeArray(D), mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(torch.from_numpy(cin).to(dev)), alpha=0.5,
+             beta=2.0, bias=(torch.from_numpy(bias).to(dev), "col"), activation="relu")
+    mb.synchronize_status(dev)
+    want = ho.fused_epilogue(raw, 0.5, 2.0, cin, bias, "col", "relu")
+    assert ho.max_rel_err(D.cpu().numpy(), want) <= TOL_F32X3

@@ -102,3 +102,72 @@ def test_static_entry_point_rejects_what_does_not_fit(mb, dev):
     assert call(16, 256, 64, a_stride=[1, 16]) == -3                                    # not K-major
     assert lib.moye_b200_gemm_skinny_static(None, None, None, ctypes.c_float(1.0), None, st) == -1
     torch.cuda.synchronize()
+
+
+def test_static_entry_point_allocates_nothing(mb, ho, dev):
+    """The contract in its name: device memory before and after a call is the same to the byte (operands, output
+    and the first-call set-up are done beforehand)."""
+    M, N, K = 16, 4096, 2048
+    X, W = _operands(ho, M, N, K, dev)
+    got = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert _static_call(mb, got, X, W, 1.0, status, dev) == 0     # warm-up: the once-per-device set-up happens here
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(3):
+        assert _static_call(mb, got, X, W, 1.0, status, dev) == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(dev)
+    assert free1 == free0
+    # the status word kept inside the array (device_status == NULL) can be read back without allocating either
+    lib = mb._lib.load()
+    T = lambda t: mb._lib.make_tensor(t.data_ptr(), mb.TORCH_TO_MOYE[t.dtype], list(t.shape), list(t.stride()))
+    assert lib.moye_b200_gemm_skinny_static(ctypes.byref(T(got)), ctypes.byref(T(X)), ctypes.byref(T(W)),
+                                            ctypes.c_float(1.0), None, mb.current_stream_ptr(dev)) == 0
+    site = ctypes.c_int32(-1)
+    assert lib.moye_b200_gemm_skinny_static_status(mb.current_stream_ptr(dev), ctypes.byref(site)) == 0 and site.value == 0
+    mb.gemm_skinny_static_status(dev)
+    free2, _ = torch.cuda.mem_get_info(dev)
+    assert free2 == free0
+
+
+_NO_HANDLE_SCRIPT = r"""
+import ctypes, sys
+import numpy as np
+import torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/oracle")
+import __graft_entry__ as ge
+import host_oracle as ho
+mb = ge.load_package()
+lib = mb._lib.load()
+dev = torch.device("cuda", 0)
+torch.cuda.set_device(dev)
+M, N, K = 16, 1024, 1024
+x, w = ho.normal_bf16_bits(9, (M * K,), 0.02), ho.normal_bf16_bits(10, (N * K,), 0.02)
+X = torch.from_numpy(x.view(np.int16)).to(dev).view(torch.bfloat16).view(M, K)
+W = torch.from_numpy(w.view(np.int16)).to(dev).view(torch.bfloat16).view(N, K)
+Y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+T = lambda t: mb._lib.make_tensor(t.data_ptr(), mb.TORCH_TO_MOYE[t.dtype], list(t.shape), list(t.stride()))
+st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+for _ in range(2):
+    rc = lib.moye_b200_gemm_skinny_static(ctypes.byref(T(Y)), ctypes.byref(T(X)), ctypes.byref(T(W)), ctypes.c_float(1.0), None, st)
+    assert rc == 0, lib.moye_b200_last_error()
+site = ctypes.c_int32(-1)
+assert lib.moye_b200_gemm_skinny_static_status(st, ctypes.byref(site)) == 0 and site.value == 0
+assert not mb._lib._handles, "a handle was created"
+ref = ho.gemm_samples(x, w, ho.BF16, M, N, K, np.arange(M, dtype=np.int32), threads=4)
+err = ho.max_rel_err(Y.float().cpu().numpy(), ref)
+assert err <= 1e-2, err
+print("NO_HANDLE_OK")
+"""
+
+
+def test_static_entry_point_needs_no_handle(dev):
+    """A fresh process that loads the library and calls only the static entry point -- `moye_b200_create` never
+    runs -- gets the oracle's result."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", _NO_HANDLE_SCRIPT, root], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "NO_HANDLE_OK" in res.stdout, res.stdout + res.stderr
