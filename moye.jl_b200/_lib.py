@@ -59,7 +59,10 @@ class CopyParams(ctypes.Structure):
                 ("flags", ctypes.c_int32)]
 
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libmoye_b200.so")
+# MOYE_B200_DEBUG=1 selects the debug build of the same library (`build.py --debug`): identical entry points, with
+# the kernels' address arithmetic checked on the device (a violation is reported through moye_b200_status).
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib",
+                        "libmoye_b200_debug.so" if os.environ.get("MOYE_B200_DEBUG") == "1" else "libmoye_b200.so")
 
 EXPORTS = {
     "moye_b200_create": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p)]),

@@ -117,7 +117,7 @@ def copyto_(*args, stream=None):
     return dst
 
 
-_AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.E4M3: "E4M3", _lib.F32: "TF32"}
+_AB_TAG = {_lib.F16: "F16", _lib.BF16: "BF16", _lib.S8: "S8", _lib.U8: "U8", _lib.E4M3: "E4M3", _lib.F32: "TF32"}
 
 
 def _epilogue(bias, activation, D, dev):
@@ -206,7 +206,7 @@ def matmul(A, B, C, **kw):
     product runs on the atom of that width."""
     A, B, C = (x if isinstance(x, MoYeArray) else MoYeArray(x) for x in (A, B, C))
     if A.dtype not in _AB_TAG:
-        raise _lib.MoyeError(-2, "matmul takes f16, bf16, f32 (as tf32), s8 or e4m3 operands on sm_100a")
+        raise _lib.MoyeError(-2, "matmul takes f16, bf16, f32, s8, u8 or e4m3 operands on sm_100a")
     tile_n = kw.pop("tile_n", 0)
     if tile_n == 0:
         return gemm_(C, A, B, None, **kw)

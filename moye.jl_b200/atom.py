@@ -107,14 +107,15 @@ _register_sm80()
 
 
 def sm100_mma_op(ab, n=256):
-    """The tcgen05 op for operand type `ab` ("F16", "BF16", "S8", "E4M3", or "TF32" for Float32
+    """The tcgen05 op for operand type `ab` ("F16", "BF16", "S8", "U8", "E4M3", or "TF32" for Float32
     storage read with a 10-bit mantissa) and tile N.
     One instruction covers 128 x n x K (K = 32 bytes of the operand type); one thread issues
     it and the accumulator lives in tensor memory, hence thr_id = 1:0 and value layouts that
     span the whole tile."""
-    acc = "S32" if ab == "S8" else "F32"
+    acc = "S32" if ab in ("S8", "U8") else "F32"
     k = 16 if ab in ("F16", "BF16") else (8 if ab == "TF32" else 32)
-    kind = {"F16": "kind::f16", "BF16": "kind::f16", "S8": "kind::i8", "E4M3": "kind::f8f6f4", "TF32": "kind::tf32"}[ab]
+    kind = {"F16": "kind::f16", "BF16": "kind::f16", "S8": "kind::i8", "U8": "kind::i8", "E4M3": "kind::f8f6f4",
+            "TF32": "kind::tf32"}[ab]
     name = f"MMAOP_SM100_128x{n}x{k}_{acc}{ab}{ab}{acc}_SS"
     if name not in MMA_OPS:
         MMA_OPS[name] = MMAOp(name, (128, n, k), _TAG[acc], _TAG[ab], _TAG[ab], _TAG[acc], L(1),
@@ -122,7 +123,7 @@ def sm100_mma_op(ab, n=256):
     return MMA_OPS[name]
 
 
-for _ab in ("F16", "BF16", "S8", "E4M3", "TF32"):
+for _ab in ("F16", "BF16", "S8", "U8", "E4M3", "TF32"):
     for _n in (64, 128, 256):
         sm100_mma_op(_ab, _n)
 

@@ -170,6 +170,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
 #pragma unroll 1
   for (int c = 0; c < BN / SC; ++c) {
     uint8_t* sb = my_buf + (nstore % NBUF) * EPI_BUF;
+    // plain epilogue: the tensor-memory read of this chunk is in flight while the warp waits for its staging buffer
+    constexpr bool EARLY_LD = MODE == EPI_PLAIN;
+    uint32_t v0[EARLY_LD ? 32 : 1];
+    if constexpr (EARLY_LD) tmem_ld_x32(t_addr + c * SC, v0);
     if (lane == 0) tma_store_wait_read<NBUF - 1>();  // the store that last used `sb` has drained
     __syncwarp();
 #pragma unroll
@@ -196,8 +200,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
         }
         if (q + 1 < BN / 32) request_others(q + 1);
       } else if constexpr (!RED) {
-        tmem_ld_x32(t_addr + col0, v);
-        tmem_ld_wait();
+        if (s == 0) {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v0[j];
+        } else {
+          tmem_ld_x32(t_addr + col0, v);
+          tmem_ld_wait();
+        }
       }
       if (((FIX || RED) ? (fx->release && fx->own_in_tmem) : RELEASE) && c == BN / SC - 1 && s == SUB - 1) {
         // last read of this accumulator: hand it back to the MMA warp

@@ -176,6 +176,9 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     const bool plain = g.beta == 0.f && g.act == 0 && g.bias_mode != 2;
     const float alpha = g.alpha;
     const int passes = rows_per / RSTEP;
+    // debug build: the largest element offset that belongs to D (and to C)
+    [[maybe_unused]] const long long d_last = (long long)(g.M - 1) * g.d_sm + (long long)(g.N - 1) * g.d_sn;
+    [[maybe_unused]] const long long c_last = (long long)(g.M - 1) * g.c_sm + (long long)(g.N - 1) * g.c_sn;
     auto reduce = [&](auto s_tag) {
       constexpr int SS = decltype(s_tag)::value;
       constexpr int UNR = SS == 8 ? 2 : 4;  // passes whose loads are in flight together
@@ -193,6 +196,10 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
           const int gm = mi * BM + row0 + (ps + u) * RSTEP;
           if (ps + u >= passes || gm >= g.M || count <= 0) continue;
           const long long off = (long long)gm * g.d_sm + (long long)gn * g.d_sn;
+          if (!MOYE_DBG_OK(off >= 0 && off + (long long)(count - 1) * g.d_sn <= d_last, g.status, 951)) continue;
+          if (!MOYE_DBG_OK(g.beta == 0.f || (g.C != nullptr && (long long)gm * g.c_sm + (long long)(gn + count - 1) * g.c_sn <= c_last),
+                           g.status, 952))
+            continue;
           if constexpr (INT_OUT) {
             int acc[4] = {0, 0, 0, 0};
 #pragma unroll

@@ -26,6 +26,17 @@ __device__ __forceinline__ uint32_t lane_id() {
   return l;
 }
 
+// ---------------------------------------------------------------- debug build (-DMOYE_DEBUG)
+// The debug library checks what the release build trusts: every global address a kernel forms by hand, every TMA
+// coordinate, tensor-memory column and pipeline stage index.  A violation records `site` in the status word (the
+// first one wins) and the access is skipped; nothing traps.  moye_b200_status() then reports MOYE_ERR_TIMEOUT-like
+// failure with that site code.  In the release build the checks compile to nothing.
+#ifdef MOYE_DEBUG
+#define MOYE_DBG_OK(cond, status, site) ((cond) ? true : (atomicCAS((status), 0, (site)), false))
+#else
+#define MOYE_DBG_OK(cond, status, site) (true)
+#endif
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
