@@ -28,6 +28,11 @@ def f32_as_accurate_as_host(ho, got, host32, exact64):
     assert ho.max_rel_err(got, host32) <= 2e-3
 
 
+def kw_of(kind):
+    """Float32 operands are compared with the oracle on tf32-truncated operands: ask for the single tf32 product."""
+    return {"allow_tf32": True} if kind == "f32" else {}
+
+
 def dev_bits(bits, dtype, shape, dev):
     t = torch.from_numpy(bits.view(np.int16) if bits.dtype == np.uint16 else bits).to(dev)
     return t.view(dtype).view(*shape)
