@@ -11,7 +11,7 @@ there is no collective in the timed region.
 Rank 0 prints ONE JSON line.  `value` is whole-job TFLOP/s with the operands resident in HBM
 (CUDA events on the launching stream, max over ranks); `e2e` is the same product through the
 package's public call with pinned HOST buffers, host<->device copies inside the timed region;
-`roofline` compares the kernel with the measured cuBLAS bf16 peak of this pool;
+`roofline` compares the kernel with the measured cuBLAS bf16 peak (MEASURED_PEAKS.json);
 `cpu_baseline` times the CPU restatement of the reference's host path on a bounded sample.
 
 `--impl reference` times only the reference's host implementation (the CPU restatement under
@@ -53,10 +53,16 @@ WORKLOADS = {
     "gemm_f16_4096x8192x4096": ("f16", 4096, 8192, 4096, "f32"),
     # the same for the 256 x 512 tile kernel: 37 x 8 = 296 tiles = 4 full waves of the 74 SM pairs, 211 MB
     "gemm_f16_9472x4096x2048": ("f16", 9472, 4096, 2048, "f32"),
-    # Float32 storage on the tf32 tensor-core kind, column-major like examples/gemm.jl (its literal element type)
+    # Float32 storage, column-major like examples/gemm.jl (its literal element type): three tf32 products of the
+    # operands' high and low parts (Float32 accuracy), and ONE tf32 product (allow_tf32, about 1e-3 relative)
     "gemm_f32_8192_colmajor": ("f32", 8192, 8192, 8192, "f32"),
+    "gemm_f32_8192_colmajor_tf32": ("f32", 8192, 8192, 8192, "f32"),
     # a few hundred rows against a mid-sized weight matrix: 32 output tiles, the case of the split-K cluster kernel
     "gemm_bf16_256x4096x4096": ("bf16", 256, 4096, 4096, "bf16"),
+    # 3.46 waves of 256 x 512 tiles: the last wave is cut along K over all CTA pairs (320 MB on the device)
+    "gemm_f16_4096x8192x8192": ("f16", 4096, 8192, 8192, "f32"),
+    # the elementwise copyto!(dst, src) through two layouts and the layout function itself, 2^24 elements
+    "layout_copy_f32_4096": ("layout", 4096, 4096, 0, "f32"),
 }
 
 
@@ -150,6 +156,18 @@ def make_operands(torch, kind, M, N, K, out, dev, seed, colmajor=False):
     if colmajor:
         A, B, C = A.t().contiguous().t(), B.t().contiguous().t(), C.t().contiguous().t()
     return A, B, C
+
+
+def gemm_kw(name):
+    kind = WORKLOADS[name][0]
+    kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
+    if name.endswith("_tf32"):
+        kw["allow_tf32"] = True
+    return kw
+
+
+def is_colmajor(name):
+    return "_colmajor" in name
 
 
 def time_launches(torch, fn, steps, warmup, stream):
@@ -267,7 +285,7 @@ def run_reference_arm(args):
 def workload_config(name, gpus):
     kind, M, N, K, out = WORKLOADS[name]
     return {"workload": name, "M_per_gpu": M, "N": N, "K": K, "global_M": M * gpus,
-            "layout": "A,B,D column-major (MN-major, as examples/gemm.jl)" if name.endswith("_colmajor") else "A,B K-major (TN); D row-major",
+            "layout": "A,B,D column-major (MN-major, as examples/gemm.jl)" if is_colmajor(name) else "A,B K-major (TN); D row-major",
             "in": kind, "out": out, "sharding": f"M-sharded x{gpus}, B replicated, no collective",
             "l2": "operands+output exceed the 126 MB L2 (no flush needed)" if M * K + N * K > 64e6
             else "operand/output buffer sets rotated, more than 512 MB in total"}
@@ -307,6 +325,8 @@ def run_ours(args):
 
     if kind in ("copy", "transpose"):
         return run_copy(args, mb, torch, dev, peaks, peak_src, rank, world, dist, barrier, transpose=kind == "transpose")
+    if kind == "layout":
+        return run_layout(args, mb, torch, dev, peaks, peak_src)
 
     # operands that would sit in the 126 MB L2 are rotated over enough buffer sets to exceed it several times
     rotate = not (M * K + N * K > 64e6)
@@ -314,12 +334,16 @@ def run_ours(args):
     sets = []
     while True:
         sets.append(make_operands(torch, kind, M, N, K, out, dev, seed=3 + rank + 16 * len(sets),
-                                  colmajor=name.endswith("_colmajor")))
+                                  colmajor=is_colmajor(name)))
         set_bytes += sum(t.numel() * t.element_size() for t in sets[-1])
         if not rotate or set_bytes > 512e6:
             break
     A, B, C = sets[0]
-    kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
+    kw = gemm_kw(name)
+    if args.path:
+        kw["path"] = args.path
+    if args.tail != "auto":
+        kw["tail"] = args.tail == "on"
     plans = [mb.plan_gemm(mb.MoYeArray(c), mb.MoYeArray(a), mb.MoYeArray(b), None, **kw) for a, b, c in sets]
     plan = plans[0]                               # the argument marshalling of gemm_ done once per buffer set
     stream_ptr = mb.current_stream_ptr(dev)
@@ -353,11 +377,16 @@ def run_ours(args):
     bytes_bound = kind == "bf16" and M <= 512
 
     # end to end: pinned host operands -> device -> GEMM -> pinned host result, every step, through the
-    # package's host pipeline (copies and kernel on three streams over two device buffer sets)
+    # package's host pipeline (copies and kernel on three streams over two device buffer sets).  With several
+    # ranks the replicated B crosses PCIe once, on rank 0, and reaches the others over NVLink (NCCL broadcast
+    # through the library's communicator); every rank copies its own A shard in and its C shard out.
+    comm = mb.Communicator(rank, world, dev) if world > 1 else None
+    if args.no_e2e:
+        return print_kernel_only(args, rank, world, name, kind, M, N, K, ms, ms_max, value, clocks, peaks, peak_src, comm, dist)
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
     hC = [torch.empty(C.shape, dtype=C.dtype).pin_memory() for _ in range(2)]
     e2e_steps = max(2, min(args.steps, 48))  # enough steps to amortise filling and draining the three-stream pipeline
-    pipe = mb.HostGemmPipeline(M, N, K, A.dtype, C.dtype, dev, depth=2, **kw)
+    pipe = mb.HostGemmPipeline(M, N, K, A.dtype, C.dtype, dev, depth=2, comm=comm, **kw)
     for i in range(3):
         pipe.submit(hA, hB, hC[i % 2])
     pipe.join()
@@ -389,11 +418,12 @@ def run_ours(args):
     e1.record(stream)
     barrier()
     e2e_serial_ms = e0.elapsed_time(e1) / 4
-    h2d = A.numel() * A.element_size() + B.numel() * B.element_size()
-    d2h = C.numel() * C.element_size()
+    a_bytes, b_bytes = A.numel() * A.element_size(), B.numel() * B.element_size()
+    h2d = a_bytes * world + b_bytes          # whole job: every rank's A shard, B once
+    d2h = C.numel() * C.element_size() * world
 
     if bytes_bound:
-        alg_bytes = h2d + d2h
+        alg_bytes = a_bytes + b_bytes + C.numel() * C.element_size()
         achieved, peak, unit, bound = alg_bytes / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
         metric, munit = "decode GEMM GB/s", "GB/s"
         value = alg_bytes * world / (ms_max * 1e-3) / 1e9
@@ -417,7 +447,11 @@ def run_ours(args):
         "data": "synthetic", "config": workload_config(name, world), "clocks": clocks, "gpu_launches": args.steps,
         "e2e": {"value": e2e_val, "unit": munit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "how": "HostGemmPipeline: H2D, GEMM, D2H on three streams, two device buffer sets; every step copies its own operands in and its result out",
+                "how": "HostGemmPipeline: H2D, GEMM, D2H on three streams, two device buffer sets; every step copies its own "
+                       "operands in and its result out" + ("; B is copied in by rank 0 only and broadcast over NVLink (NCCL)"
+                                                            if world > 1 else ""),
+                "bytes_are": "summed over all ranks", "h2d_bytes_rank0": a_bytes + b_bytes,
+                "h2d_bytes_other_ranks": a_bytes if world > 1 else None, "nvlink_bcast_bytes_per_step": b_bytes if world > 1 else 0,
                 "serial_ms_per_step": e2e_serial_ms},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peak_kind}, of {peak_src}",
@@ -426,24 +460,12 @@ def run_ours(args):
                      "kernel_ms": ms},
     }
     if dist is not None and world > 1 and not args.no_extras and not bytes_bound:
-        # outside the timed path: reassembling the M-sharded C on every rank over NCCL, reported on its own
         try:
-            mb.all_gather_rows(C, M * world, world)
-            barrier()
-            e0.record(stream)
-            for _ in range(3):
-                full = mb.all_gather_rows(C, M * world, world)
-            e1.record(stream)
-            barrier()
-            t = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            shard_bytes = C.numel() * C.element_size()
-            line["allgather_c"] = {"ms": float(t.item()), "shard_bytes": shard_bytes,
-                                   "busbw_GB/s": shard_bytes * (world - 1) / float(t.item()) / 1e6,
-                                   "how": "torch.distributed all_gather (NCCL) of the row shards + concatenation, not in `value`"}
-            del full
+            line.update(multi_gpu_extras(mb, torch, dist, comm, dev, rank, world, name, A, B, C, barrier, peaks))
         except Exception as exc:  # reported, never hidden
-            line["allgather_c"] = {"error": repr(exc)}
+            line["multi_gpu_extras_error"] = repr(exc)
+    if comm is not None:
+        comm.destroy()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ho, _ = ge.load_oracle()
         threads = os.cpu_count() or 1
@@ -455,6 +477,8 @@ def run_ours(args):
             "other_configs": cpu_other_configs(ho, np, threads)}
     if rank == 0 and world == 1 and not args.no_extras:
         line["also"] = extras(mb, torch, dev, peaks)
+        if not bytes_bound:
+            line["also"]["sustained"] = sustained_rate(mb, torch, dev, plan, stream_ptr, flops_of(kind, M, N, K), peaks)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -462,19 +486,223 @@ def run_ours(args):
     return 0
 
 
+def print_kernel_only(args, rank, world, name, kind, M, N, K, ms, ms_max, value, clocks, peaks, peak_src, comm, dist):
+    """`--no-e2e`: the device-timed figure alone (what a profiler capture of one kernel needs; not a bench line)."""
+    line = {"kernel_only": True, "workload": name, "ms_per_step": ms_max, "TFLOP/s": value, "n_gpus": world,
+            "path": args.path, "tail": args.tail, "clocks": clocks, "config": workload_config(name, world)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_layout(args, mb, torch, dev, peaks, peak_src):
+    """The elementwise `copyto!(dst, src)` through two different layouts (a transposing pair) and the evaluation of
+    the layout function, 2^24 elements each: integer index arithmetic per element, reported as GB/s of the bytes
+    moved (4 + 4 per element for the copy, 8 written per element for the evaluation)."""
+    m = n = 4096
+    src = torch.rand(m * n, device=dev)
+    dst = torch.zeros_like(src)
+    stream = torch.cuda.current_stream()
+    a_dst = mb.MoYeArray(dst, mb.make_layout((m, n), (n, 1)))     # row-major destination
+    a_src = mb.MoYeArray(src, mb.make_layout(((64, 64), n), ((1, 64 * n), 64)))   # a hierarchical source layout
+    steps, warm = args.steps, max(3, args.warmup)
+    ms_copy = time_launches(torch, lambda: mb.copyto_(a_dst, a_src, elementwise_ok=True), steps, warm, stream)
+    lay = mb.make_layout((8, (4, 2), 16, 16384), (3, (64, 7), 1, 4096))
+    ms_eval = time_launches(torch, lambda: mb.layout_eval(lay, device=dev), steps, warm, stream)
+    mb.synchronize_status(dev)
+    res = {"layout_copy": {"ms": ms_copy, "GB/s": 8.0 * m * n / ms_copy / 1e6},
+           "layout_eval": {"ms": ms_eval, "GB/s": 8.0 * m * n / ms_eval / 1e6}}
+    line = {"metric": "layout copy GB/s", "value": res["layout_copy"]["GB/s"], "unit": "GB/s", "n_gpus": 1, "steps": steps,
+            "warmup": warm, "ms_per_step": ms_copy, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 (bytes) / int64 indices", "data": "synthetic", "config": {"workload": "layout_copy_f32_4096"},
+            "gpu_launches": 2 * steps, "kernels": res,
+            "roofline": {"bound": "hbm", "achieved": res["layout_copy"]["GB/s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": res["layout_copy"]["GB/s"] / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": f"hbm copy, of {peak_src}"}}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def max_ms(torch, dist, dev, ms):
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def multi_gpu_extras(mb, torch, dist, comm, dev, rank, world, name, A, B, C, barrier, peaks):
+    """Outside the timed headline, at N > 1 GPUs: the all-gather of the M-sharded C through the library's own entry
+    point, the splits the configurations state (one product cut into M / N rows per GPU; the decode weights cut
+    along N; the copy cut into row blocks), each timed on the device as the max over ranks, and a parity check of
+    this rank's shard against the CPU oracle."""
+    import numpy as np
+    import __graft_entry__ as ge
+    out = {}
+    stream = torch.cuda.current_stream()
+    sp = mb.current_stream_ptr(dev)
+    kind, M, N, K, o = WORKLOADS[name]
+
+    def timed(fn, n=10, w=3):
+        for _ in range(w):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        barrier()
+        return max_ms(torch, dist, dev, e0.elapsed_time(e1) / n)
+
+    # (1) all-gather of C: every rank's (M, N) row-major shard into a preallocated (world*M, N) matrix, NCCL behind
+    # moye_b200_allgather; checked against the shards themselves
+    full = torch.empty(M * world, N, dtype=C.dtype, device=dev)
+    ms = timed(lambda: comm.allgather(C, full, mode=0), n=5, w=2)
+    shard_bytes = C.numel() * C.element_size()
+    mine_ok = bool(torch.equal(full[rank * M:(rank + 1) * M], C))
+    sums = torch.stack([full[r * M:(r + 1) * M].double().abs().sum() for r in range(world)])
+    own = torch.zeros(world, dtype=torch.float64, device=dev)
+    own[rank] = C.double().abs().sum()
+    dist.all_reduce(own)
+    ok = torch.tensor([1.0 if (mine_ok and bool(torch.equal(sums, own))) else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    full[rank * M:(rank + 1) * M].copy_(C)
+    ms_in_place = timed(lambda: comm.allgather(full[rank * M:(rank + 1) * M], full, mode=0), n=5, w=2)
+    out["allgather_c"] = {"ms": ms, "shard_bytes": shard_bytes, "busbw_GB/s": shard_bytes * (world - 1) / ms / 1e6,
+                          "in_place_ms": ms_in_place, "in_place_busbw_GB/s": shard_bytes * (world - 1) / ms_in_place / 1e6,
+                          "assembled_equals_shards": bool(ok.item() == 1.0),
+                          "how": "moye_b200_allgather (ncclAllGather into a preallocated matrix), not in `value`"}
+    del full
+
+    # (2) parity of this rank's shard of the headline product: 8 of its rows against the CPU oracle
+    ho, _ = ge.load_oracle()
+    ho.lib()
+    rows = np.linspace(0, M - 1, 8).astype(np.int32)
+    if kind in ("f16", "bf16"):
+        bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16).ravel()
+        ref = ho.gemm_samples(bits(A), bits(B), ho.F16 if kind == "f16" else ho.BF16, M, N, K, rows, by_rows=True,
+                              threads=min(16, os.cpu_count() or 1))
+        err = ho.max_rel_err(C[torch.from_numpy(rows).to(dev).long()].float().cpu().numpy(), ref)
+        good = torch.tensor([1.0 if err <= 1e-2 else 0.0], device=dev)
+        dist.all_reduce(good, op=dist.ReduceOp.MIN)
+        out["shard_parity"] = bool(good.item() == 1.0)
+        out["shard_parity_how"] = "8 rows of every rank's C shard against the CPU oracle (max relative error <= 1e-2)"
+
+    # (3) strong scaling as the configurations state it: ONE product, M / world rows per GPU, B replicated
+    strong = {}
+    for wl in ("gemm_f16_8192", "gemm_f16_4096"):
+        k2, M2, N2, K2, o2 = WORKLOADS[wl]
+        lo, hi = mb.shard_range(M2, world, rank, 256)
+        a2, b2, c2 = make_operands(torch, k2, M2, N2, K2, o2, dev, seed=40)   # same seed: every rank holds the same problem
+        plan_full = mb.plan_gemm(c2, a2, b2, None)
+        plan_shard = mb.plan_gemm(c2[lo:hi], a2[lo:hi], b2, None)
+        t_shard = timed(lambda: plan_shard(sp), n=20, w=5)
+        t_full = timed(lambda: plan_full(sp), n=10, w=3)     # the whole product on every GPU at once: the N = 1 time
+        # this rank's shard against the same rows of the whole product (the split of K over CTA pairs may differ
+        # between the two launches, so fp32 sums agree to rounding, not bit for bit)
+        plan_full(sp)
+        whole = c2.clone()
+        c2.zero_()
+        plan_shard(sp)
+        diff = ((c2[lo:hi] - whole[lo:hi]).abs().max() / whole.abs().max()).item()
+        same = torch.tensor([1.0 if diff <= 1e-5 else 0.0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        fl = 2.0 * M2 * N2 * K2
+        strong[wl] = {"rows_per_gpu": hi - lo, "ms": t_shard, "TFLOP/s": fl / t_shard / 1e9, "n1_ms": t_full,
+                      "n1_TFLOP/s": fl / t_full / 1e9, "efficiency": t_full / (world * t_shard),
+                      "shards_match_whole_product": bool(same.item() == 1.0)}
+        del a2, b2, c2, whole, plan_full, plan_shard
+        torch.cuda.empty_cache()
+    out["strong"] = strong
+
+    # (4) decode: W cut into N / world rows per GPU, X replicated; Y column-major so that a rank's columns are one
+    # contiguous block; the all-gather of Y timed on its own
+    k5, M5, N5, K5, o5 = WORKLOADS["decode_bf16_16x28672x8192"]
+    lo, hi = mb.shard_range(N5, world, rank, 128)
+    sets = [make_operands(torch, k5, M5, hi - lo, K5, o5, dev, seed=50 + i) for i in range(3)]   # rotate W: HBM, not L2
+    ys = [torch.zeros(hi - lo, M5, dtype=torch.bfloat16, device=dev).t() for _ in sets]
+    plans = [mb.plan_gemm(y, x, w, None) for (x, w, _), y in zip(sets, ys)]
+    turn = [0]
+
+    def decode_step():
+        turn[0] += 1
+        plans[turn[0] % len(plans)](sp)
+
+    t_dec = timed(decode_step, n=20, w=5)
+    nbytes = (M5 * K5 + N5 * K5 + M5 * N5) * 2
+    yfull = torch.zeros(N5, M5, dtype=torch.bfloat16, device=dev).t()
+    t_gather = timed(lambda: comm.allgather(ys[0], yfull, mode=1, align=128), n=10, w=3)
+    out["decode_nshard"] = {"rows_of_W_per_gpu": hi - lo, "ms": t_dec, "GB/s": nbytes / t_dec / 1e6,
+                            "frac_of_hbm_peak_per_gpu": nbytes / world / t_dec / 1e6 / peaks["hbm_gbs"],
+                            "allgather_y_ms": t_gather, "allgather_y_bytes": M5 * N5 * 2,
+                            "y_block_matches": bool(torch.equal(yfull[:, lo:hi], ys[0]))}
+    del sets, ys, plans, yfull
+    torch.cuda.empty_cache()
+
+    # (5) copy: the 8192 x 8192 fp16 column-major matrix cut into blocks of 8192 / world rows (pitched sub-matrices)
+    m = n = 8192
+    lo, hi = mb.shard_range(m, world, rank, 128)
+    srcs = [(torch.rand(n, m, device=dev) * 2 - 1).half() for _ in range(4)]
+    dsts = [torch.zeros_like(x) for x in srcs]
+    lay = mb.make_layout((hi - lo, n), (1, m))
+    tc = mb.make_tma_tiled_copy(mb._lib.F16, (128, 64))
+    cps = [mb.plan_copy(tc, mb.MoYeArray(d[:, lo:hi], lay), mb.MoYeArray(x[:, lo:hi], lay)) for d, x in zip(dsts, srcs)]
+
+    def copy_step():
+        turn[0] += 1
+        cps[turn[0] % 4](sp)
+
+    t_cp = timed(copy_step, n=20, w=5)
+    good = torch.tensor([1.0 if torch.equal(dsts[1][:, lo:hi], srcs[1][:, lo:hi]) else 0.0], device=dev)
+    dist.all_reduce(good, op=dist.ReduceOp.MIN)
+    out["copy_rowblock"] = {"rows_per_gpu": hi - lo, "ms": t_cp, "GB/s": 2.0 * m * n * 2 / t_cp / 1e6,
+                            "frac_of_hbm_peak_per_gpu": 2.0 * m * n * 2 / world / t_cp / 1e6 / peaks["hbm_gbs"],
+                            "bit_exact": bool(good.item() == 1.0)}
+    mb.synchronize_status(dev)
+    return out
+
+
+def sustained_rate(mb, torch, dev, plan, stream_ptr, flops, peaks, seconds=2.0):
+    """The headline GEMM back to back for `seconds`: what the part delivers under its power limit, with the SM
+    clock it settles at."""
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(20):
+        plan(stream_ptr)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    n = max(50, int(seconds * 1e3 / (e0.elapsed_time(e1) / 20)))
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    e0.record(stream)
+    for _ in range(n):
+        plan(stream_ptr)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / n
+    tf = flops / ms / 1e9
+    return {"launches": n, "ms": ms, "TFLOP/s": tf, "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"],
+            "sm_mhz_median": clocks["sm_mhz"], "ms_x_mhz": ms * clocks["sm_mhz"] if clocks["sm_mhz"] else None,
+            "reasons": clocks["reasons"]}
+
+
 def extras(mb, torch, dev, peaks):
     """The other configurations, each timed alone for a few launches (reported beside the headline)."""
     out = {}
     stream = torch.cuda.current_stream()
     for name in ("gemm_f16_4096", "gemm_f16_8192_colmajor", "gemm_bf16_8192", "gemm_f32_8192_colmajor",
-                 "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192",
-                 "gemm_bf16_256x4096x4096"):
+                 "gemm_f32_8192_colmajor_tf32", "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192",
+                 "decode_bf16_16x28672x8192", "gemm_bf16_256x4096x4096"):
         kind, M, N, K, o = WORKLOADS[name]
         nset = 3 if M <= 32 else (12 if M <= 512 else 1)  # rotate weight buffers for the HBM-bound shapes
-        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i, colmajor=name.endswith("_colmajor"))
+        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=20 + i, colmajor=is_colmajor(name))
                 for i in range(nset)]
-        kw = {"scale_a": 0.05, "scale_b": 0.02} if kind == "e4m3" else {}
-        plans = [mb.plan_gemm(c, a, b, None, **kw) for a, b, c in sets]
+        plans = [mb.plan_gemm(c, a, b, None, **gemm_kw(name)) for a, b, c in sets]
         sp = mb.current_stream_ptr(dev)
         i = [0]
 
@@ -586,6 +814,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm_f16_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="device-timed kernel only (for profiler captures)")
+    ap.add_argument("--path", type=int, default=0, help="force a GEMM kernel (moye_gemm_params_t.path); 0 = the library's choice")
+    ap.add_argument("--tail", choices=["auto", "on", "off"], default="auto", help="K-split tail of the 256 x 512 kernel")
     args = ap.parse_args()
     if args.steps < 1:
         raise SystemExit("--steps must be >= 1")

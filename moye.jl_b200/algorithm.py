@@ -20,7 +20,7 @@ from .array import MoYeArray, isgmem
 from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
 from .layout import Layout, coalesce, size
 
-__all__ = ["copyto_", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
+__all__ = ["copyto_", "copy_dispatch", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
            "gemm_skinny_static_", "gemm_skinny_static_status", "plan_gemm", "plan_copy", "LaunchPlan", "axpby_"]
 
 
@@ -61,8 +61,41 @@ def _tensor_arg(x, what):
     return x._abi
 
 
-def copyto_(*args, stream=None):
-    """`copyto!(dst, src)` or `copyto!(tiled_copy, dst, src)` on global-memory arrays."""
+def copy_dispatch(dst, src, tiled_copy=None):
+    """Which device path a `copyto!` takes, decided on the host from shapes, strides and alignment alone:
+    "tiled" (`moye_b200_copy`: 128-bit / TMA tiles, or the transposing kernel) or "elementwise"
+    (`moye_b200_layout_copy`: one index computation per element through both layouts).  Returns (path, reason);
+    `reason` says why two rank-2 arrays that look tileable are not (None otherwise)."""
+    sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
+    if sd_d is None or sd_s is None or sd_d[0] != sd_s[0]:
+        return "elementwise", None
+    same_first = sd_d[1][0] == 1 and sd_s[1][0] == 1
+    one_unit_each = tiled_copy is None and 1 in sd_d[1] and 1 in sd_s[1]
+    if not (same_first or one_unit_each):
+        return "elementwise", None
+    eb = dst.elem_bytes
+    for x, sd in ((dst, sd_d), (src, sd_s)):
+        if x.ptr % 16:
+            return "elementwise", "a base address is not 16-byte aligned"
+        pitch = [st for sh, st in zip(sd[0], sd[1]) if st != 1 and sh > 1]
+        if any((st * eb) % 16 for st in pitch):
+            return "elementwise", "a pitch is not a multiple of 16 bytes"
+    if not same_first and eb not in (1, 2, 4, 8):
+        return "elementwise", "the transposing kernel moves elements of 1, 2, 4 or 8 bytes"
+    return "tiled", None
+
+
+_warned_slow_copy = set()
+
+
+def copyto_(*args, stream=None, elementwise_ok=False):
+    """`copyto!(dst, src)` or `copyto!(tiled_copy, dst, src)` on global-memory arrays.
+
+    With a TiledCopy the tiled kernel runs or the call fails.  Without one the meaning is the reference's elementwise
+    copy through both layouts (src/algorithm/copy.jl:4-16); two rank-2 arrays of equal shape, each contiguous along
+    one mode and 16-byte aligned, take the tiled kernels, everything else the per-element kernel.  The choice is made
+    here, on the host (`copy_dispatch`): no call is tried and retried.  When only alignment keeps two matrices off the
+    fast path a warning says so once per reason, unless `elementwise_ok=True`."""
     if len(args) == 3:
         tiled_copy, dst, src = args
     else:
@@ -82,30 +115,32 @@ def copyto_(*args, stream=None):
             raise TypeError("first argument must be a TiledCopy")
         mode = tiled_copy.copy_atom.op.mode
         if mode is None:
-            raise _lib.MoyeError(-3, f"{tiled_copy.copy_atom.op} is narrower than 128 bits; the device copy kernels "
-                                     "move 128-bit atoms or TMA tiles")
+            raise _lib.MoyeError(-3, f"{tiled_copy.copy_atom.op} has no device copy kernel: the kernels move 128-bit "
+                                     "atoms or TMA tiles (ldmatrix atoms feed registers inside a kernel; on sm_100a "
+                                     "operands reach the tensor cores through TMA and shared-memory descriptors)")
         tm, tn = tiled_copy.tiler_mn[0], tiled_copy.tiler_mn[1] if len(tiled_copy.tiler_mn) > 1 else 1
         if mode == _lib.COPY_UNIVERSAL128:
             # the tiler of one pass is (threads x vector) wide; the kernel loops it over a CTA tile of
             # 64 columns like the reference's copy kernel loops its partition
             tn = max(tn, 64)
         params = _lib.CopyParams(mode, tm, tn, 0)
-    sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
-    tiled_ok = (sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0] and sd_d[1][0] == 1 and sd_s[1][0] == 1)
-    # one unit stride each, in different modes (`copyto!(dest, transpose(src))`) or both in the second mode: the
-    # library picks the transposing kernel or swaps the modes; explicit tiled copies keep the reference's contract
-    other_ok = (tiled_copy is None and not tiled_ok and sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0]
-                and 1 in sd_d[1] and 1 in sd_s[1])
-    if tiled_ok or other_ok:
+        sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
+        if not (sd_d is not None and sd_s is not None and sd_d[0] == sd_s[0] and sd_d[1][0] == 1 and sd_s[1][0] == 1):
+            raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode")
+        path = "tiled"
+    else:
+        path, reason = copy_dispatch(dst, src)
+        if reason is not None and not elementwise_ok and reason not in _warned_slow_copy:
+            import warnings
+            _warned_slow_copy.add(reason)
+            warnings.warn(f"copyto!: {reason}; these matrices take the per-element kernel, which is many times slower "
+                          "than the tiled one (pass elementwise_ok=True to silence this)", RuntimeWarning, stacklevel=2)
+    if path == "tiled":
+        sd_d, sd_s = _as_rank2(dst), _as_rank2(src)
         td = _lib.make_tensor(dst.ptr, dst.dtype, sd_d[0], sd_d[1])
         ts = _lib.make_tensor(src.ptr, src.dtype, sd_s[0], sd_s[1])
-        rc = lib.moye_b200_copy(h, ctypes.byref(td), ctypes.byref(ts), ctypes.byref(params) if params else None, st)
-        if rc == 0:
-            return dst
-        if tiled_copy is not None or rc not in (-5, -3):
-            _lib.check(rc)
-    elif tiled_copy is not None:
-        raise _lib.MoyeError(-3, "a tiled copy needs rank-2 operands of equal shape, contiguous along the first mode")
+        _lib.check(lib.moye_b200_copy(h, ctypes.byref(td), ctypes.byref(ts), ctypes.byref(params) if params else None, st))
+        return dst
     # elementwise through both layouts
     ds, dd = dst.layout.flat()
     ss, sdd = src.layout.flat()

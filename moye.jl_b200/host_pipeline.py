@@ -16,7 +16,10 @@ __all__ = ["HostGemmPipeline"]
 
 
 class HostGemmPipeline:
-    def __init__(self, M, N, K, in_dtype, out_dtype, device=None, depth=2, **gemm_kw):
+    def __init__(self, M, N, K, in_dtype, out_dtype, device=None, depth=2, comm=None, **gemm_kw):
+        """`comm` (a `Communicator`) makes B a replicated operand of several ranks: only rank 0 copies it from the
+        host, the others receive it over NVLink (`moye_b200_bcast`), which takes N - 1 copies of B off the PCIe links."""
+        self.comm = comm
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.depth = depth
         d = self.device
@@ -48,7 +51,10 @@ class HostGemmPipeline:
             if reuse:
                 self.s_in.wait_event(self.mm_done[k])     # the GEMM that last read A[k], B[k] has finished
             self.A[k].copy_(A_host, non_blocking=True)
-            self.B[k].copy_(B_host, non_blocking=True)
+            if self.comm is None or self.comm.rank == 0:
+                self.B[k].copy_(B_host, non_blocking=True)
+            if self.comm is not None:
+                self.comm.bcast(self.B[k], 0, stream=ctypes.c_void_p(self.s_in.cuda_stream))
             self.in_ready[k].record(self.s_in)
         self.s_mm.wait_event(self.in_ready[k])
         if reuse:
