@@ -13,6 +13,7 @@ from .atom import *  # noqa: F401,F403
 from .algorithm import *  # noqa: F401,F403
 from .sharding import *  # noqa: F401,F403
 from .host_pipeline import *  # noqa: F401,F403
+from .printing import *  # noqa: F401,F403
 from ._lib import MoyeError
 
 __version__ = "0.1.0"

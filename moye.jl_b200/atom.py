@@ -101,6 +101,14 @@ def _register_sm80():
         if name == "MMAOP_8x8x16_S32S8S8S32_TN":
             lb = L(((4, 8), 2), ((32, 1), 8))  # reference src/traits/mma_sm80.jl:104-111 special case
         MMA_OPS[name] = MMAOp(name, mnk, _TAG[d], _TAG[a], _TAG[b], _TAG[c], L(32), la, lb, lc, "sm_80")
+    # the tf32 warp ops of the tensor-core manual (reference src/traits/mma_sm80.jl:104-111): Float32 storage
+    f32 = _lib.F32
+    MMA_OPS["MMAOP_16x8x8_F32TF32TF32F32_TN"] = MMAOp(
+        "MMAOP_16x8x8_F32TF32TF32F32_TN", (16, 8, 8), f32, f32, f32, f32, L(32),
+        L(((4, 8), (2, 2)), ((16, 1), (8, 64))), L(((4, 8), 2), ((8, 1), 32)), L(((4, 8), (2, 2)), ((32, 1), (16, 8))), "sm_80")
+    MMA_OPS["MMAOP_16x8x4_F32TF32TF32F32_TN"] = MMAOp(
+        "MMAOP_16x8x4_F32TF32TF32F32_TN", (16, 8, 4), f32, f32, f32, f32, L(32),
+        L(((4, 8), 2), ((16, 1), 8)), L(((4, 8), 1), ((8, 1), 8)), L(((4, 8), (2, 2)), ((32, 1), (16, 8))), "sm_80")
 
 
 _register_sm80()
@@ -203,6 +211,26 @@ class TiledMMA:
             tv = self.thrfrg_B(make_layout((ts[1], ts[2])))
             tile = (COLON, (make_layout((size(thr, 1), size(thr, 2)), (0, 1)), COLON))
         return composition(composition(tv, (tile, COLON)), (inv, COLON))
+
+    def _layout_mn(self, which):
+        """(layout over the tile -> index into (thr, val), thread-id layout) (reference src/atom/mma.jl:236-262)."""
+        ts, thr = self.tile_shape(), self.thr_layout_vmnk
+        if which == "C":
+            ref, tv, thrid = make_layout((ts[0], ts[1])), self.thrfrg_C, thr(COLON, COLON, COLON, 1)
+        elif which == "A":
+            ref, tv, thrid = make_layout((ts[0], ts[2])), self.thrfrg_A, thr(COLON, COLON, 1, COLON)
+        else:
+            ref, tv, thrid = make_layout((ts[1], ts[2])), self.thrfrg_B, thr(COLON, 1, COLON, COLON)
+        return composition(right_inverse(tv(ref)), make_layout(ref.shape)), thrid
+
+    def get_layoutC_MN(self):
+        return self._layout_mn("C")
+
+    def get_layoutA_MK(self):
+        return self._layout_mn("A")
+
+    def get_layoutB_NK(self):
+        return self._layout_mn("B")
 
     def get_layoutA_TV(self):
         return self._layout_tv("A")
@@ -370,6 +398,28 @@ class TiledCopy:
         a = self.copy_atom
         return self._tile2thrfrg(zipped_divide(dst, self.tiler_mn),
                                  composition(right_inverse(a.val_layout_ref), a.val_layout_dst))
+
+    def _layout_tv_of(self, val_layout):
+        """(thr, val) -> offset in the tile (reference src/atom/copy.jl:168-174,184-190)."""
+        ref = make_layout((self.tiler_mn, 1))
+        tv = self._tile2thrfrg(ref, composition(right_inverse(self.copy_atom.val_layout_ref), val_layout))
+        return tv(COLON, COLON, 1)
+
+    def get_layoutS_TV(self):
+        return self._layout_tv_of(self.copy_atom.val_layout_src)
+
+    def get_layoutD_TV(self):
+        return self._layout_tv_of(self.copy_atom.val_layout_dst)
+
+    def _layout_mn_of(self, tv):
+        return composition(right_inverse(tv), make_layout(self.tiler_mn)), make_layout(size(self.tiled_layout_tv, 0))
+
+    def get_layoutS_MN(self):
+        """(layout over the tile -> index into (thr, val), thread-id layout) (reference src/atom/copy.jl:176-182)."""
+        return self._layout_mn_of(self.get_layoutS_TV())
+
+    def get_layoutD_MN(self):
+        return self._layout_mn_of(self.get_layoutD_TV())
 
     def get_slice(self, thr_idx):
         return ThrCopy(self, thr_idx)

@@ -20,7 +20,7 @@ __all__ = [
     "composition", "complement", "right_inverse", "left_inverse", "logical_product", "zipped_product",
     "tiled_product", "blocked_product", "raked_product", "tile_to_shape", "logical_divide", "zipped_divide",
     "tiled_divide", "upcast", "downcast", "recast_layout", "make_fragment_like", "max_common_vector",
-    "get_congr_coord", "append_layout", "prepend_layout", "group_modes", "Swizzle", "print_layout",
+    "get_congr_coord", "append_layout", "prepend_layout", "group_modes", "Swizzle", "ComposedLayout", "print_layout",
 ]
 
 COLON = ":"
@@ -348,13 +348,16 @@ def make_ordered_layout(shape, order=None):
 
 
 def size(l, *modes):
-    s = l.shape if isinstance(l, Layout) else l
+    s = l.shape if isinstance(l, (Layout, ComposedLayout)) else l
     for m in modes:
         s = s[m]
     return product(s)
 
 
 def cosize(l):
+    if isinstance(l, ComposedLayout):
+        block = 1 << (l.swizzle.bits + l.swizzle.base + abs(l.swizzle.shift))
+        return -(-(cosize(l.layout) + l.offset) // block) * block
     return l(size(l))
 
 
@@ -452,7 +455,14 @@ def _compose(ls, ld, rs, rd):
 
 
 def composition(lhs, rhs):
-    """`lhs ∘ rhs`: R(c) = lhs(rhs(c)) (reference src/layout.jl:520-608)."""
+    """`lhs ∘ rhs`: R(c) = lhs(rhs(c)) (reference src/layout.jl:520-608).  `lhs` may be a `Swizzle` (the result is a
+    `ComposedLayout`) or a `ComposedLayout` (the right-hand side composes with its inner layout)."""
+    if isinstance(lhs, Swizzle):
+        if not isinstance(rhs, Layout):
+            rhs = make_layout(rhs)
+        return ComposedLayout(lhs, rhs)
+    if isinstance(lhs, ComposedLayout):
+        return ComposedLayout(lhs.swizzle, composition(lhs.layout, rhs), lhs.offset)
     if rhs == COLON:
         return lhs
     if isinstance(rhs, Layout):
@@ -675,10 +685,11 @@ def make_fragment_like(l):
 
 # ------------------------------------------------------------------------------ swizzle
 class Swizzle:
-    """The XOR swizzle functor `Swizzle{B,M,S}`: bits [M+S, M+S+B) of an offset are XOR-ed
-    into bits [M, M+B).  MoYe lists bank-conflict swizzling as missing (reference
-    README.md:14-17); the B200 kernels need it because TMA and tcgen05 agree on the
-    128-byte pattern `Swizzle(3, 4, 3)` over byte offsets."""
+    """The XOR swizzle functor `Swizzle{B,M,S}`: bits [M+S, M+S+B) of a 0-based offset are XOR-ed into bits
+    [M, M+B).  MoYe lists bank-conflict swizzling as missing (reference README.md:14-17); the B200 kernels need
+    it because TMA and tcgen05 agree on the 128-byte pattern `Swizzle(3, 4, 3)` over byte offsets.  A swizzle
+    composes with a layout: `Swizzle(3, 4, 3) @ layout` (or `composition(swizzle, layout)`) is the layout
+    function followed by the XOR, a `ComposedLayout`."""
 
     __slots__ = ("bits", "base", "shift")
 
@@ -691,15 +702,82 @@ class Swizzle:
         mask = ((1 << self.bits) - 1) << (self.base + self.shift)
         return offset0 ^ ((offset0 & mask) >> self.shift)
 
+    def __matmul__(self, other):
+        return composition(self, other)
+
+    def __eq__(self, other):
+        return isinstance(other, Swizzle) and (self.bits, self.base, self.shift) == (other.bits, other.base, other.shift)
+
+    def __hash__(self):
+        return hash((self.bits, self.base, self.shift))
+
     def __repr__(self):
         return f"Swizzle({self.bits},{self.base},{self.shift})"
+
+
+class ComposedLayout:
+    """`swizzle ∘ offset ∘ layout`: the offset of `layout`, shifted by a constant, then XOR-swizzled.  Everything
+    about the domain (shape, rank, size, slicing a mode, composing with another layout on the right) is the inner
+    layout's; only the value changes.  Evaluation is 1-based like `Layout`: `(S ∘ L)(i) = S(L(i) - 1 + offset) + 1`.
+    The image of a swizzle is a permutation of aligned blocks of 2^(M+S+B) offsets, so `cosize` is the inner
+    layout's rounded up to such a block."""
+
+    __slots__ = ("swizzle", "offset", "layout")
+
+    def __init__(self, swizzle, layout, offset=0):
+        if not isinstance(swizzle, Swizzle) or not isinstance(layout, Layout):
+            raise TypeError("ComposedLayout(Swizzle, Layout[, offset])")
+        self.swizzle, self.layout, self.offset = swizzle, layout, int(offset)
+
+    shape = property(lambda self: self.layout.shape)
+    stride = property(lambda self: self.layout.stride)
+
+    def __call__(self, *coord):
+        if len(coord) == 1:
+            coord = coord[0]
+        inner = self.layout(coord)
+        if isinstance(inner, Layout):  # a slice: the kept modes, the fixed ones folded into the offset
+            return ComposedLayout(self.swizzle, inner, self.offset + self.layout(_first_coord(coord, self.layout.shape)) - 1)
+        return self.swizzle(inner - 1 + self.offset) + 1
+
+    def offset0(self, idx0):
+        return self.swizzle(self.layout.offset0(idx0) + self.offset)
+
+    def __getitem__(self, i):
+        return ComposedLayout(self.swizzle, self.layout[i], self.offset)
+
+    def __len__(self):
+        return len(self.layout)
+
+    def __eq__(self, other):
+        return (isinstance(other, ComposedLayout) and self.swizzle == other.swizzle and self.layout == other.layout
+                and self.offset == other.offset)
+
+    def __hash__(self):
+        return hash((self.swizzle, self.layout, self.offset))
+
+    def __matmul__(self, other):
+        return composition(self, other)
+
+    def __repr__(self):
+        off = f" o {self.offset}" if self.offset else ""
+        return f"{self.swizzle!r}{off} o {self.layout!r}"
+
+
+def _first_coord(coord, shape):
+    """`coord` with every colon replaced by the first coordinate of its mode (all ones)."""
+    if coord == COLON:
+        return tuple(_first_coord(COLON, s) for s in shape) if _is_t(shape) else 1
+    if _is_t(coord):
+        return tuple(_first_coord(c, s) for c, s in zip(coord, shape))
+    return coord
 
 
 def print_layout(layout, file=None):
     """`print_layout(layout)` for a rank-2 layout: the table of 1-based indices, rows = mode 1, columns = mode 2
     (reference src/print.jl:7-44, same cell widths and rulers).  Returns the text as well."""
     if len(layout) != 2:
-        raise ValueError("print_layout takes a rank-2 layout")
+        raise ValueError("print_layout takes a rank-2 layout (a swizzled one is fine)")
     rows, cols = size(layout[0]), size(layout[1])
     w = len(str(cosize(layout))) + 2
     rule = "    " + ("+-----------------"[:w + 1]) * cols + "+"

@@ -17,7 +17,21 @@ def _load(name):
 
 
 def test_example_gemm():
-    assert _load("gemm").test() < 2e-3
+    assert _load("gemm").test() < 1e-5
+
+
+def test_example_pipeline():
+    """docs/src/manual/pipeline.md:89-202 on the tcgen05 atoms."""
+    ex = _load("pipeline")
+    assert ex.host_side()["tAgA"] == ((2, 1), 2, 1, 32)
+    assert ex.test() < 1e-5
+
+
+def test_example_tensor_core():
+    """docs/src/manual/tensor_core.md:265-391 (TF32, make_tiled_copy_A / _B, ldmatrix atom) on the kind::tf32 atom."""
+    ex = _load("tensor_core")
+    assert ex.host_side()["threads"] == 128
+    assert ex.test() < 1e-5
 
 
 def test_example_transpose_and_copy():

@@ -299,3 +299,120 @@ def test_print_layout_table(mb):
     assert text == want and buf.getvalue() == want + "\n"
     wide = mb.print_layout(mb.make_layout(((2, 2), 4), ((1, 8), 2)), file=io.StringIO()).splitlines()
     assert wide[2] == "    +----+----+----+----+" and wide[3] == " 1  |  1 |  3 |  5 |  7 |"
+
+
+def test_swizzle_composes_with_layouts(mb):
+    """`Swizzle ∘ Layout` as part of the algebra (the gap reference README.md:14-17 names): the composed layout
+    reproduces, offset for offset, the XOR the kernels' epilogue and TMA's SWIZZLE_128B mode use."""
+    sw = mb.Swizzle(3, 4, 3)
+    rows = mb.make_layout((32, 128), (128, 1))              # 32 staging rows of 128 bytes, byte offsets
+    tile = sw @ rows
+    assert isinstance(tile, mb.ComposedLayout) and tile == mb.composition(sw, rows)
+    assert mb.size(tile) == 4096 and mb.cosize(tile) == 4096 and len(tile) == 2 and tile.shape == (32, 128)
+    # the 1024 16-byte stores of the GEMM epilogue: row `lane`, 16-byte group j -> rowp + ((j ^ (lane & 7)) << 4)
+    for lane in range(32):
+        for j in range(8):
+            for b in range(4):   # four bytes inside the group, so 1024 offsets in all
+                assert tile(lane + 1, 16 * j + 4 * b + 1) - 1 == lane * 128 + ((j ^ (lane & 7)) << 4) + 4 * b
+    assert tile.offset0(5 * 1 + 0) == sw(rows.offset0(5))   # 0-based form
+    # a swizzle permutes offsets inside aligned 1024-byte blocks: the image of the tile is the tile
+    assert sorted(tile(i) for i in range(1, 4097)) == list(range(1, 4097))
+    # slicing keeps the swizzle and folds the fixed coordinate into the offset; composing on the right reaches inside
+    col = tile(mb.COLON, 17)
+    assert [col(r) for r in (1, 2, 9)] == [tile(r, 17) for r in (1, 2, 9)]
+    sub = tile @ mb.make_layout((8, 8), (1, 512))           # rows 0..7 x every 16th byte
+    assert all(sub(r, c) == tile(r, 16 * (c - 1) + 1) for r in range(1, 9) for c in range(1, 9))
+    assert tile[1] == mb.ComposedLayout(sw, mb.make_layout(128, 1))
+    # the K-major operand stage of the tensor-core kernels is the same function over (row, k) of 16-bit elements
+    stage = mb.umma_smem_layout(mb._lib.F16, 128, "K")
+    assert stage(9, 1) - 1 == 8 * 128 and stage(2, 1) - 1 == 128 + 16 and stage(2, 9) - 1 == 128
+    mn = mb.umma_smem_layout(mb._lib.F16, 128, "MN")         # chunks of 64 elements along M, K rows 128 bytes apart
+    assert mn((1, 2), 1) - 1 == 64 * 128 and mn((9, 1), 2) - 1 == 128 + (16 ^ 16)
+    text = mb.print_layout(mb.Swizzle(2, 0, 3) @ mb.make_layout((8, 8), (8, 1)), file=open(os.devnull, "w"))
+    assert "| 10 |  9 | 12 | 11 |" in text and text.startswith("Swizzle(2,0,3) o (8, 8):(8, 1)")
+    with pytest.raises(ValueError):
+        mb.Swizzle(3, 4, 2)
+    with pytest.raises(TypeError):
+        mb.ComposedLayout(rows, rows)
+
+
+def test_ownership_pictures(mb):
+    """`print_typst` for a TiledCopy / TiledMMA (reference src/print.jl:317-345) and the tcgen05 views."""
+    import io
+    # the thread map the manual draws (docs/src/manual/tiled_matmul.md:9-16): thr (32,8) x val (4,1) on a (128,8) tile
+    tc = mb.make_tiled_copy(mb.CopyAtom(mb.UniversalCopy(128), mb._lib.F32), mb.make_layout((32, 8)), mb.make_layout((4, 1)))
+    lay, thr = tc.get_layoutS_MN()
+    n = len(tc)
+    for m in range(128):
+        for c in range(8):
+            idx0 = lay(m + 1, c + 1) - 1
+            assert (idx0 % n, idx0 // n) == (m // 4 + 32 * c, m % 4)
+    assert tc.get_layoutD_MN()[0] == lay and mb.size(thr) == 256
+    text = mb.print_typst(tc, file=io.StringIO())
+    assert text.count("owner(") == 2 * 128 * 8 + 1 and "owner(33, 2)," in text
+    # the tf32 configuration of the tensor-core manual (docs/src/manual/tensor_core.md:358-366)
+    mma = mb.make_tiled_mma(mb.mma_op("MMAOP_16x8x8_F32TF32TF32F32_TN"), mb.make_layout((2, 2, 1), (2, 1, 1)), (32, 32, 8))
+    assert len(mma) == 128 and mma.tile_shape() == (32, 32, 8)
+    c_mn, c_thr = mma.get_layoutC_MN()
+    owners = {}
+    for m in range(1, 33):
+        for nn in range(1, 33):
+            idx0 = c_mn(m, nn) - 1
+            owners.setdefault(c_thr(idx0 % mb.size(c_thr) + 1) - 1, []).append(idx0 // mb.size(c_thr))
+    assert sorted(owners) == list(range(128)) and all(sorted(v) == list(range(8)) for v in owners.values())
+    text = mb.print_typst(mma, file=io.StringIO())
+    assert text.count("owner(") == 32 * 32 + 2 * 32 * 8 + 1
+    # a tcgen05 atom: one issuing thread owns everything; the informative pictures are where the data lives
+    op = mb.sm100_mma_op("F16", 128)
+    text = mb.print_typst(mb.make_tiled_mma(op), file=io.StringIO())
+    assert text.count("owner(0, ") == 128 * 128 + 2 * 128 * 16
+    text = mb.print_tmem_layout(op, cta_pair=True, file=io.StringIO())
+    assert "128 x 2 CTAs lanes x 128 columns" in text and "warp%4=3" in text
+    assert mb.tmem_accumulator_layout(128, cta_pair=True)(130, 5) == (1, 1, 4)
+    text = mb.print_umma_smem_layout(mb._lib.F16, 8, "K", file=io.StringIO())
+    assert "    1     c1      c0      c3      c2      c5      c4      c7      c6" in text
+    with pytest.raises(ValueError):
+        mb.print_tmem_layout(mb.mma_op("MMAOP_16x8x16_F32F16F16F32_TN"))
+
+
+def test_copy_dispatch_is_decided_on_the_host(mb):
+    """`copyto_` never tries one kernel and falls back to another: shapes, strides and alignment decide up front."""
+    base = torch.zeros(64 * 1024 + 64, dtype=torch.float16)
+    full = mb.MoYeArray(base[:64 * 1024], mb.make_layout((256, 256)))
+    assert mb.copy_dispatch(full, full) == ("tiled", None)
+    rowm = mb.MoYeArray(base[:64 * 1024], mb.make_layout((256, 256), (256, 1)))
+    assert mb.copy_dispatch(full, rowm) == ("tiled", None)                           # contiguous along different modes: transpose
+    odd = mb.MoYeArray(base[1:64 * 1024 + 1], mb.make_layout((256, 256)))
+    assert mb.copy_dispatch(full, odd) == ("elementwise", "a base address is not 16-byte aligned")
+    pitched = mb.MoYeArray(base, mb.make_layout((250, 256), (1, 257)))
+    path, why = mb.copy_dispatch(mb.MoYeArray(base, mb.make_layout((250, 256), (1, 256))), pitched)
+    assert path == "elementwise" and "pitch" in why
+    hier = mb.MoYeArray(base[:64 * 1024], mb.make_layout(((16, 16), 256), ((1, 4096), 16)))
+    assert mb.copy_dispatch(full, hier) == ("elementwise", None)                     # not a rank-2 strided matrix at all
+    diff = mb.MoYeArray(base[:32 * 1024], mb.make_layout((128, 256)))
+    assert mb.copy_dispatch(full, diff)[0] == "elementwise"
+
+
+def test_manual_kernel_variants_host_side(mb):
+    """The objects the reference manual builds for its pipelined and tensor-core kernels, evaluated on the host:
+    the partition shapes are the ones its comments state (docs/src/manual/pipeline.md:105-128,
+    tensor_core.md:283-312,352-381)."""
+    import importlib.util
+    ex = {}
+    for name in ("pipeline", "tensor_core"):
+        spec = importlib.util.spec_from_file_location("example_" + name, os.path.join(os.path.dirname(__file__), "..", "examples", name + ".py"))
+        ex[name] = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ex[name])
+    p = ex["pipeline"].host_side()
+    assert p["threads"] == 256 and p["blocks"] == (16, 16) and p["mma_tile"] == (32, 8, 1)
+    assert p["gA"] == (128, 8, 32) and p["gC"] == (128, 128)                       # (bM, bK, k), (bM, bN)
+    assert p["tAgA"] == ((2, 1), 2, 1, 32) and p["tAsA"] == ((2, 1), 2, 1, 2)      # (CPY, CPY_M, CPY_K, k | 2)
+    assert p["tCsA"] == (1, 4, 8, 2) and p["tCsB"] == (1, 16, 8, 2) and p["tCgC"] == (1, 4, 16)   # (MMA, MMA_M|N, MMA_K, 2)
+    assert p["tCrA"] == (1, 4, 8) and p["tCrC"] == (1, 4, 16) and p["k_tile_max"] == 32 and p["k_block_max"] == 8
+    assert p["smem_floats"] == 2 * ((128 + 2) * 8 * 2 - 2)                          # two padded (bM, bK, 2) buffers
+    t = ex["tensor_core"].host_side()
+    assert t["threads"] == 128 and t["mma_tile"] == (32, 32, 8)
+    assert t["gmem_copy_A_tiler"] == (64, 8) and t["gmem_copy_B_tiler"] == (32, 16)
+    assert t["smem_copy_A_tiler"] == (32, 8) and t["smem_copy_B_tiler"] == (32, 8) and t["smem_copy_threads"] == (128, 128)
+    assert t["tCsA"] == ((2, 2), 4, 2, 2) and t["tCsB"] == (2, 8, 2, 2)
+    assert mb.size(mb.make_layout(t["tCsA_retiled"])) == mb.size(mb.make_layout(t["tCsA"]))
