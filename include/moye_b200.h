@@ -198,6 +198,19 @@ int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t*
 int moye_b200_copy(moye_handle_t h, const moye_tensor_t* dst, const moye_tensor_t* src,
                    const moye_copy_params_t* params, void* stream);
 
+/* `copyto!(tiled_copy, dst, src)` for a TiledCopy on an ldmatrix atom (`LDSM_U32x{1,2,4}_N`, `LDSM_U16x{2,4,8}_T`;
+ * reference src/arch/copy/ldmatrix.jl:18-96, src/traits/ldmatrix.jl:1-41), as in the kernel of the reference's
+ * device test (test/device/tiled_copy.jl:2-23): one tile of 16-bit elements, `span` elements long in memory
+ * (at most 24576), is staged in shared memory; each of `threads` threads (a multiple of 32) loads `iters`
+ * fragments with `ldmatrix` (`matrices` = 1, 2 or 4, `transposed` = .trans) and stores the 2 * matrices values of
+ * every fragment to global memory.  The two tables are HOST arrays of element offsets inside the tile, evaluated
+ * by the caller from `partition_S` / `partition_D`: src_offsets[t * iters + i] is the first of the 8 contiguous
+ * values of thread t's i-th source fragment (16-byte aligned), dst_offsets[(t * iters + i) * 2 * matrices + v]
+ * where its v-th received value goes.  dst and src are device pointers to the tile's first element. */
+int moye_b200_ldsm_copy(moye_handle_t h, void* dst, const void* src, int32_t span, int32_t matrices,
+                        int32_t transposed, int32_t threads, int32_t iters, const int32_t* src_offsets,
+                        const int32_t* dst_offsets, void* stream);
+
 /* dst[Ld(i)] = src[Ls(i)] for i in 1:size(Ls), any two layouts of equal size: the
  * elementwise `copyto!(dst, src)` of reference src/algorithm/copy.jl:4-16,42-64 evaluated
  * on the device.  elem_bytes in {1,2,4,8,16}. */

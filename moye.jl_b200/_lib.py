@@ -16,6 +16,7 @@ F32, F16, BF16, S8, U8, E4M3, S32, U16, U32, U64, U128 = range(11)
 DTYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, U8: 1, E4M3: 1, S32: 4, U16: 2, U32: 4, U64: 8, U128: 16}
 
 COPY_AUTO, COPY_UNIVERSAL128, COPY_TMA, COPY_TRANSPOSE = 0, 1, 2, 3
+COPY_LDSM = 100  # host-side tag of the ldmatrix tiled copy (its own entry point, moye_b200_ldsm_copy)
 
 STATUS_NAMES = {
     0: "OK", -1: "INVALID_ARG", -2: "UNSUPPORTED_DTYPE", -3: "UNSUPPORTED_LAYOUT", -4: "UNSUPPORTED_SHAPE",
@@ -92,6 +93,9 @@ EXPORTS = {
     "moye_b200_allgather": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.POINTER(Tensor),
                                            ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]),
     "moye_b200_bcast": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Tensor), ctypes.c_int32, ctypes.c_void_p]),
+    "moye_b200_ldsm_copy": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                           ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                           ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32), ctypes.c_void_p]),
     "moye_b200_layout_eval": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(FlatLayout), ctypes.c_int64,
                                              ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
 }

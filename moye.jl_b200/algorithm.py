@@ -114,10 +114,11 @@ def copyto_(*args, stream=None, elementwise_ok=False):
         if not isinstance(tiled_copy, TiledCopy):
             raise TypeError("first argument must be a TiledCopy")
         mode = tiled_copy.copy_atom.op.mode
+        if mode == _lib.COPY_LDSM:
+            return _ldsm_copy(tiled_copy, dst, src, lib, h, st)
         if mode is None:
             raise _lib.MoyeError(-3, f"{tiled_copy.copy_atom.op} has no device copy kernel: the kernels move 128-bit "
-                                     "atoms or TMA tiles (ldmatrix atoms feed registers inside a kernel; on sm_100a "
-                                     "operands reach the tensor cores through TMA and shared-memory descriptors)")
+                                     "atoms, TMA tiles or ldmatrix fragments")
         tm, tn = tiled_copy.tiler_mn[0], tiled_copy.tiler_mn[1] if len(tiled_copy.tiler_mn) > 1 else 1
         if mode == _lib.COPY_UNIVERSAL128:
             # the tiler of one pass is (threads x vector) wide; the kernel loops it over a CTA tile of
@@ -149,6 +150,27 @@ def copyto_(*args, stream=None, elementwise_ok=False):
     ld, ls = _lib.make_flat_layout(ds, dd), _lib.make_flat_layout(ss, sdd)
     _lib.check(lib.moye_b200_layout_copy(h, ctypes.c_void_p(dst.ptr), ctypes.byref(ld), ctypes.c_void_p(src.ptr),
                                          ctypes.byref(ls), dst.elem_bytes, st))
+    return dst
+
+
+def _ldsm_copy(tiled_copy, dst, src, lib, h, st):
+    """`copyto!(tiled_copy, dst, src)` for an ldmatrix TiledCopy: dst and src are the same tile layout over two
+    buffers (the `t_g_in` / `t_g_out` of reference test/device/tiled_copy.jl:2-23); the tile goes through shared
+    memory and every thread's `ldmatrix` fragments."""
+    from .atom import ldsm_tiled_copy_tables
+    if dst.elem_bytes != 2:
+        raise _lib.MoyeError(-2, "ldmatrix moves 16-bit elements")
+    if dst.layout != src.layout:
+        raise _lib.MoyeError(-3, "an ldmatrix tiled copy takes source and destination with the same tile layout")
+    try:
+        span, iters, so, do = ldsm_tiled_copy_tables(tiled_copy, src.layout)
+    except ValueError as exc:
+        raise _lib.MoyeError(-3, str(exc))
+    op = tiled_copy.copy_atom.op
+    src_t = (ctypes.c_int32 * len(so))(*so)
+    dst_t = (ctypes.c_int32 * len(do))(*do)
+    _lib.check(lib.moye_b200_ldsm_copy(h, ctypes.c_void_p(dst.ptr), ctypes.c_void_p(src.ptr), span, op.matrices,
+                                       1 if op.transposed else 0, len(tiled_copy), iters, src_t, dst_t, st))
     return dst
 
 

@@ -20,7 +20,7 @@ tensor memory, so its thread-id layout is `1:0` and its "fragments" are whole ti
 """
 from . import _lib
 from .array import MoYeArray
-from .layout import (COLON, Layout, _tup, append_layout, coalesce, composition, get_congr_coord, logical_divide,
+from .layout import (COLON, Layout, _tup, append_layout, coalesce, composition, cosize, get_congr_coord, logical_divide,
                      make_layout, product_each, raked_product, right_inverse, size, tiled_product, upcast,
                      zipped_divide)
 
@@ -28,7 +28,7 @@ __all__ = [
     "MMAOp", "CopyOp", "UniversalFMA", "UniversalCopy", "CPOP_ASYNC_CACHEALWAYS", "CPOP_TMA_LOAD_SW128",
     "CPOP_TMA_STORE", "MMAAtom", "TiledMMA", "ThrMMA", "make_tiled_mma", "CopyAtom", "TiledCopy", "ThrCopy",
     "make_tiled_copy", "make_tma_tiled_copy", "make_tiled_copy_A", "make_tiled_copy_B", "make_tiled_copy_C", "MMA_OPS", "mma_op",
-    "sm100_mma_op", "DTYPE_BITS", "LDSM_OPS", "ldsm_op",
+    "sm100_mma_op", "DTYPE_BITS", "LDSM_OPS", "ldsm_op", "ldsm_tiled_copy_tables",
 ]
 
 DTYPE_BITS = {_lib.F32: 32, _lib.F16: 16, _lib.BF16: 16, _lib.S8: 8, _lib.U8: 8, _lib.E4M3: 8, _lib.S32: 32,
@@ -309,14 +309,18 @@ def CPOP_ASYNC_CACHEALWAYS(bits):
 
 
 def _ldsm(name, src, dst):
-    return CopyOp(name, L(32), src, dst, dst)
+    op = CopyOp(name, L(32), src, dst, dst, mode=_lib.COPY_LDSM)
+    op.matrices = int(name[name.index("x") + 1]) // (2 if name.endswith("_T") else 1)   # x1 / x2 / x4 of the instruction
+    op.transposed = name.endswith("_T")
+    return op
 
 
 # ldmatrix ops: 32 threads move 1 / 2 / 4 8x8 b16 matrices from shared memory to registers, optionally
 # transposed.  Bit-level (thread, bit) layouts as in reference src/traits/ldmatrix.jl:1-41 (ops:
 # src/arch/copy/ldmatrix.jl:18-48).  tcgen05 reads its operands straight from shared-memory descriptors,
-# so the B200 kernels do not issue ldmatrix; the ops exist so that TiledCopy objects built on them
-# (reference test/copy.jl:152-157, docs/src/manual/tensor_core.md) partition exactly as in MoYe.
+# so the GEMM kernels do not issue ldmatrix; a TiledCopy built on these ops (reference test/copy.jl:152-157,
+# docs/src/manual/tensor_core.md) partitions exactly as in MoYe, and `copyto_(tiled_copy, dst, src)` runs it on
+# the device as the reference's test kernel does (test/device/tiled_copy.jl:2-23, `ldsm_tiled_copy_tables`).
 LDSM_OPS = {
     "LDSM_U32x1_N": _ldsm("LDSM_U32x1_N", L(((8, 4), 128), ((128, 0), 1)), L((32, 32), (32, 1))),
     "LDSM_U32x2_N": _ldsm("LDSM_U32x2_N", L(((16, 2), 128), ((128, 0), 1)), L((32, (32, 2)), (32, (1, 1024)))),
@@ -444,6 +448,34 @@ class ThrCopy:
 
     def partition_D(self, d):
         return self._partition(d, self.tiled_copy.tidfrg_D)
+
+
+def ldsm_tiled_copy_tables(tiled_copy, tile_layout):
+    """What every thread of an ldmatrix TiledCopy does to a tile with layout `tile_layout` (16-bit elements), as
+    two tables of 0-based element offsets: `src[t][i]`, the first value of thread t's i-th source fragment in
+    `partition_S(thr_copy, tile)`, and `dst[t][i][v]`, where the v-th value it receives lands in
+    `partition_D(thr_copy, tile)` -- the `copyto!(tiled_copy, tXrX, tXsX); copyto!(tXgX, tXrX)` of the reference's
+    test kernel (test/device/tiled_copy.jl:13-20).  Returns (span, iters, src, dst) with lists of ints."""
+    import torch
+    atom = tiled_copy.copy_atom
+    nsrc, ndst = atom.num_val_src, atom.num_val_dst
+    span = int(cosize(tile_layout))
+    tile = MoYeArray(torch.zeros(1, dtype=torch.int16), tile_layout)
+    src, dst, iters = [], [], None
+    for t in range(1, len(tiled_copy) + 1):
+        thr = tiled_copy.get_slice(t)
+        s, d = thr.partition_S(tile), thr.partition_D(tile)
+        n_s, n_d = size(s.layout), size(d.layout)
+        if n_s % nsrc or n_d % ndst or n_s // nsrc != n_d // ndst:
+            raise ValueError("source and destination partitions disagree on the number of atoms")
+        iters = n_s // nsrc
+        for i in range(iters):
+            first = s.offset + s.layout(i * nsrc + 1) - 1
+            if any(s.offset + s.layout(i * nsrc + v + 1) - 1 != first + v for v in range(nsrc)):
+                raise ValueError(f"thread {t}: the {nsrc} values of a source fragment are not contiguous in the tile")
+            src.append(first)
+            dst.extend(d.offset + d.layout(i * ndst + v + 1) - 1 for v in range(ndst))
+    return span, iters, src, dst
 
 
 def make_tiled_copy(copy_atom, thr_layout, val_layout=None):

@@ -19,7 +19,7 @@ LIBDIR = os.path.join(HERE, "lib")
 OUT = os.path.join(LIBDIR, "libmoye_b200.so")
 OUT_DEBUG = os.path.join(LIBDIR, "libmoye_b200_debug.so")
 SOURCES = ["api.cu", "gemm_sm100.cu", "gemm_single.cu", "gemm_pair.cu", "gemm_wide.cu", "gemm_splitk.cu",
-           "gemm_skinny.cu", "copy_sm100.cu", "transpose_sm100.cu", "layout_sm100.cu", "axpby_sm100.cu",
+           "gemm_skinny.cu", "copy_sm100.cu", "transpose_sm100.cu", "layout_sm100.cu", "axpby_sm100.cu", "ldsm_sm100.cu",
            "comm_nccl.cu"]
 HEADERS = ["common.h", "ptx.cuh", "gemm_common.cuh", os.path.join("..", "..", "include", "moye_b200.h")]
 CFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]

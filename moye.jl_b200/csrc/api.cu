@@ -227,6 +227,8 @@ int moye_b200_destroy(moye_handle_t h) {
   if (h->workspace) cudaFree(h->workspace);
   if (h->tail_ws) cudaFree(h->tail_ws);
   if (h->split_ws) cudaFree(h->split_ws);
+  if (h->table) cudaFree(h->table);
+  if (h->table_order.done) cudaEventDestroy(h->table_order.done);
   if (h->split_order.done) cudaEventDestroy(h->split_order.done);
   if (h->sk_order.done) cudaEventDestroy(h->sk_order.done);
   if (h->tail_order.done) cudaEventDestroy(h->tail_order.done);

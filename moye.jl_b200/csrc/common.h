@@ -85,7 +85,9 @@ struct moye_b200_ctx {
   size_t tail_ws_bytes = 0;
   void* split_ws = nullptr;         // lo(A), lo(B) of the Float32 GEMM's three-product split
   size_t split_ws_bytes = 0;
-  ScratchOrder sk_order, tail_order, split_order;
+  void* table = nullptr;            // offset tables of the ldmatrix tiled copy
+  size_t table_bytes = 0;
+  ScratchOrder sk_order, tail_order, split_order, table_order;
   void* comm = nullptr;             // ncclComm_t of this rank (comm_nccl.cu), null until moye_b200_comm_init
   int comm_rank = 0, comm_world = 0;
   std::mutex mu;

@@ -86,7 +86,16 @@ __device__ __forceinline__ float load_c_as_float(const void* C, long long off) {
 // MN-major: the tile is split into chunks of 128 bytes along MN, each a box {128 B, BK rows}.
 template <int ELEM, int BK, bool MN_POSSIBLE>
 __device__ __forceinline__ void load_operand(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int mn, int row0,
-                                             int rows, int kb) {
+                                             int rows, int kb, [[maybe_unused]] int* dbg_status = nullptr) {
+#ifdef MOYE_DEBUG
+  // x (the coordinate along the contiguous mode) times the element size must be a multiple of 16 bytes, the
+  // destination 1024-byte aligned inside the stage (the 128-byte swizzle's atom), coordinates not negative
+  if (dbg_status != nullptr &&
+      (kb < 0 || row0 < 0 || ((mn ? row0 : kb * BK) * ELEM) % 16 != 0 || (smem_u32(dst) & (mn ? 127u : 1023u)) != 0)) {
+    atomicCAS(dbg_status, 0, 982);
+    return;  // the load is skipped: the consumer's bounded wait ends the kernel
+  }
+#endif
   if (!MN_POSSIBLE || !mn) {
     tma_load_2d(dst, tm, bar, kb * BK, row0);
   } else {
@@ -289,6 +298,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
     }
     fence_proxy_async_smem();
     __syncwarp();
+    // debug build: a store or reduce must not start at a negative coordinate, its x must sit on a 16-byte boundary,
+    // the staging buffer must be one of this warp's, and the tile must lie in the accumulator's columns
+    if (!MOYE_DBG_OK(m0 >= 0 && n0 + c * SC >= 0 && (((OUT_M_MAJOR ? m0 : n0 + c * SC) * (int)sizeof(OutT)) & 15) == 0 &&
+                         sb >= my_buf && sb < my_buf + NBUF * EPI_BUF && (t_addr & 0xFFFFu) + BN <= 512u,
+                     g.status, 981)) {
+      ++nstore;
+      continue;
+    }
     if (lane == 0) {
       if constexpr (RED) {
         if constexpr (OUT_M_MAJOR) tma_reduce_add_2d(tmD, sb, m0, n0 + c * SC);

@@ -94,8 +94,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             uint8_t* sa = smem + stage * STAGE_BYTES;
             if (rank == 0) {
               mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
-              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, BN / 2, kb);
+              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb, g.status);
+              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, BN / 2, kb, g.status);
             } else {
               const uint32_t leader_full = leader_full0 + stage * 8;
               mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);

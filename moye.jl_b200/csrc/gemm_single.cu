@@ -84,8 +84,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_PROD_EMPTY)) { ok = false; break; }
             mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
             uint8_t* sa = smem + stage * STAGE_BYTES;
-            load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb);
-            load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb);
+            load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb, g.status);
+            load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb, g.status);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }

@@ -96,8 +96,8 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITES_PROD_EMPTY)) break;
         mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
         uint8_t* sa = smem + stage * STAGE_BYTES;
-        load_operand<ELEM, BK, true>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb);
-        load_operand<ELEM, BK, true>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb);
+        load_operand<ELEM, BK, true>(sa, &tmA, &full[stage], g.a_mn, mi * BM, BM, kb, g.status);
+        load_operand<ELEM, BK, true>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, ni * BN, BN, kb, g.status);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }

@@ -197,8 +197,8 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             uint8_t* sa = smem + stage * STAGE_BYTES;
             if (rank == 0) {
               mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb);
-              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, 256, kb);
+              load_operand<ELEM, BK, MN>(sa, &tmA, &full[stage], g.a_mn, row_a, BM, kb, g.status);
+              load_operand<ELEM, BK, MN>(sa + A_BYTES, &tmB, &full[stage], g.b_mn, row_b, 256, kb, g.status);
             } else {
               const uint32_t leader_full = leader_full0 + stage * 8;
               mbar_arrive_expect_tx_remote(leader_full, STAGE_BYTES);

@@ -675,3 +675,24 @@ def test_float32_three_product_split(mb, ho, dev, M, N, K):
     want = ho.fused_epilogue(raw, 0.5, 2.0, cin, bias, "col", "relu")
     want64 = ho.fused_epilogue(exact, 0.5, 2.0, cin, bias, "col", "relu")   # evaluated in float64, returned as float32
     f32_as_accurate_as_host(ho, D.cpu().numpy(), want, want64)
+
+
+def test_parity_under_the_debug_build(dev):
+    """The debug library (`build.py --debug`, selected with MOYE_B200_DEBUG=1) checks on the device every global
+    address the kernels form by hand, every TMA coordinate and staging buffer, and the tensor-memory columns; a
+    violation would surface as a status code.  The small parity tests must pass under it unchanged -- this is the
+    stand-in for a memory checker on machines where none may run."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sel = ("test_small_goldens_all_dtypes or test_alpha_beta_and_low_precision_outputs or test_skinny_shapes or "
+           "(test_gemm_full_oracle and 384-520-1008) or (test_stream_k_tail_equals_whole_tiles and 300-520-1008) or "
+           "(test_float32_three_product_split and 256-512-1024)")
+    env = dict(os.environ, MOYE_B200_DEBUG="1")
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_gemm.py"),
+                          os.path.join(root, "tests", "test_gpu_layout_copy.py"), "-q", "-x", "-m", "gpu", "-k",
+                          sel + " or ldmatrix or transpos"], capture_output=True, text=True, env=env, timeout=1500)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-1000:]
+    assert "libmoye_b200_debug.so" in subprocess.run(
+        [sys.executable, "-c", "import __graft_entry__ as g; print(g.load_package()._lib.LIB_PATH)"], capture_output=True,
+        text=True, env=env, cwd=root).stdout

@@ -235,3 +235,43 @@ def test_empty_and_invalid_copies(mb, dev):
     bad = mb._lib.CopyParams(1, 24, 0, 0)  # tile_m * 2 bytes = 48 is not 16 * 2^k
     assert lib.moye_b200_copy(h, ctypes.byref(b), ctypes.byref(a), ctypes.byref(bad), st) == -1
     mb.synchronize_status(dev)
+
+
+@pytest.mark.parametrize("op", ["LDSM_U32x1_N", "LDSM_U32x2_N", "LDSM_U32x4_N"])
+def test_ldmatrix_tiled_copy_reference_device_test(mb, dev, op):
+    """The reference's own device test of its ldmatrix atoms (test/device/tiled_copy.jl:58-97): iota tiles of UInt16
+    through shared memory, `ldmatrix` per thread, registers to global memory; `g_out == g_in`."""
+    U16 = mb._lib.U16
+    cases = [(mb.make_layout((32, 32), (1, 32)), mb.make_layout((16, 2)), mb.make_layout((2, 4)), 32 * 32),
+             (mb.make_layout((32, (2, 4)), (2, (1, 64))), mb.make_layout((32, 1)), mb.make_layout((1, 8)), 32 * 8)]
+    for smem_layout, thr, val, n in cases:
+        tiled_copy = mb.make_tiled_copy(mb.CopyAtom(mb.ldsm_op(op), U16), thr, val)
+        g_in = torch.arange(1, n + 1, dtype=torch.int16, device=dev)
+        g_out = torch.zeros(n, dtype=torch.int16, device=dev)
+        mb.copyto_(tiled_copy, mb.MoYeArray(g_out, smem_layout), mb.MoYeArray(g_in, smem_layout))
+        mb.synchronize_status(dev)
+        assert torch.equal(g_out, g_in), (op, smem_layout)
+    # fp16 values and four warps: the smem -> register copy of B in the manual's tensor-core kernel
+    # (docs/src/manual/tensor_core.md:369-371), 128 threads over one (128, 16) K-major buffer
+    if op == "LDSM_U32x4_N":
+        mma = mb.make_tiled_mma(mb.mma_op("MMAOP_16x8x16_F32F16F16F32_TN"), mb.make_layout((2, 2, 1), (2, 1, 1)), (32, 32, 16))
+        smem_copy_B = mb.make_tiled_copy_B(mb.CopyAtom(mb.ldsm_op(op), mb._lib.F16), mma)
+        sB = mb.make_layout((128, 16), (16, 1))
+        src = torch.randn(128 * 16, device=dev).half()
+        dst = torch.zeros_like(src)
+        mb.copyto_(smem_copy_B, mb.MoYeArray(dst, sB), mb.MoYeArray(src, sB))
+        mb.synchronize_status(dev)
+        assert torch.equal(dst, src)
+
+
+def test_ldmatrix_tiled_copy_refuses_what_the_instruction_cannot_do(mb, dev):
+    U16 = mb._lib.U16
+    tiled_copy = mb.make_tiled_copy(mb.CopyAtom(mb.ldsm_op("LDSM_U32x1_N"), U16), mb.make_layout((16, 2)), mb.make_layout((2, 4)))
+    buf = torch.zeros(4096, dtype=torch.int16, device=dev)
+    with pytest.raises(mb.MoyeError):    # rows of the tile are 2 elements long: no fragment of 8 contiguous values
+        mb.copyto_(tiled_copy, mb.MoYeArray(buf, mb.make_layout((32, 32), (32, 1))), mb.MoYeArray(buf, mb.make_layout((32, 32), (32, 1))))
+    with pytest.raises(mb.MoyeError):    # different layouts on the two sides
+        mb.copyto_(tiled_copy, mb.MoYeArray(buf, mb.make_layout((32, 32), (1, 32))), mb.MoYeArray(buf, mb.make_layout((32, 32), (1, 64))))
+    f32 = torch.zeros(1024, device=dev)
+    with pytest.raises(mb.MoyeError):    # 32-bit elements
+        mb.copyto_(tiled_copy, mb.MoYeArray(f32, mb.make_layout((32, 32))), mb.MoYeArray(f32, mb.make_layout((32, 32))))
