@@ -17,6 +17,11 @@
  *     `@cuda` launch it replaces.  Return value: 0 on success, a negative moye_status_t
  *     otherwise; `moye_b200_last_error()` gives a thread-local message.  Nothing aborts,
  *     traps or throws across this boundary, and there is no CPU fallback.
+ *   - One handle per (host thread, device).  A handle may be used with several streams: the kernels that keep
+ *     scratch in the handle (the stream-K decode GEMM, the K-split tail of the dense kernel, the Float32 split,
+ *     the ldmatrix copy) are ordered by the library with an event whenever two of them that share a scratch
+ *     buffer come on different streams; everything else runs concurrently.  Scratch buffers are allocated once,
+ *     on first use, at their final size; only the Float32 split buffer grows with the operands.
  */
 #ifndef MOYE_B200_H
 #define MOYE_B200_H
@@ -153,8 +158,10 @@ const char* moye_b200_last_error(void);
 
 /* Synchronises `stream` and returns the device-side status word: MOYE_OK, or
  * MOYE_ERR_TIMEOUT if a bounded mbarrier wait inside a kernel gave up (the kernel then tears
- * down cleanly and the context stays usable).  `site` (may be NULL) receives the code of the
- * wait that ran out.  The reference's counterpart is `CUDA.synchronize()` after the launch
+ * down cleanly and the context stays usable: on such a report the call also waits for the whole
+ * device and puts the stream-K ticket areas of the handle back to zero, which a kernel that gave
+ * up may have left half counted).  `site` (may be NULL) receives the code of the wait that ran
+ * out (in the debug build also the code of a failed device-side address check, 951-982).  The reference's counterpart is `CUDA.synchronize()` after the launch
  * (reference test/device/matmul.jl:80). */
 int moye_b200_status(moye_handle_t h, void* stream, int32_t* site);
 
@@ -178,9 +185,13 @@ int moye_b200_selftest_dirty_tickets(moye_handle_t h, void* stream);
  * (src/algorithm/copy.jl:42-64), the `gemm!` tower (src/algorithm/blas.jl:11-131) and the
  * epilogue `copyto!(gC, rC)` (examples/gemm.jl:62), on tcgen05 tensor cores.
  * Supported (A,B -> accum -> D): f16,f16 -> f32 -> f32|f16; bf16,bf16 -> f32 -> f32|bf16;
- * s8,s8 -> s32 -> s32 (bit-exact); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b;
- * f32,f32 -> f32 -> f32 on the tf32 tensor-core kind (operands are read with a 10-bit mantissa, the
- * accumulation is fp32: the Float32 arrays of examples/gemm.jl run as they are, to about 1e-3 relative).
+ * s8|u8,s8|u8 -> s32 -> s32 (bit-exact; signed and unsigned may be mixed, reference S32U8S8S32 ... ops,
+ * src/arch/mma/make_mma_ops.jl:143-160); e4m3,e4m3 -> f32 -> bf16|f32 with scale_a*scale_b;
+ * f32,f32 -> f32 -> f32 on the tf32 tensor-core kind: by default to Float32 accuracy (three products of the
+ * operands' high and low parts, D = lo(A).B + A.lo(B) + A.B, as accurate as the host's fp32 gemm!; rows of A and
+ * B must be 16-byte multiples; a handle-owned buffer of the operands' size holds the low parts), with
+ * MOYE_GEMM_ALLOW_TF32 one product (operands read with a 10-bit mantissa, about 1e-3 relative, three times faster).
+ * The Float32 arrays of examples/gemm.jl run as they are.
  * A and B may each be K-major (stride 1 along K) or MN-major (stride 1 along M / N: MoYe's
  * column-major arrays, the storage of examples/gemm.jl:92-93), for every operand type.
  * D may be M-major or N-major.  The strided mode's pitch must be a multiple of 16 bytes.
