@@ -154,11 +154,13 @@ struct FixUp {
 // TMEM -> registers -> (alpha, beta, convert) -> staging tile in shared memory -> TMA store.
 // After the last TMEM read the accumulator is handed back: an arrive on `acc_empty_local`, or,
 // when `acc_empty_remote` is non-zero, on that shared::cluster address (the pair leader's barrier).
-template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int NBUF = 2, bool RELEASE = true, int MODE = EPI_PLAIN>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorMap* tmD, uint32_t t_addr, int m0,
-                                              int n0, uint8_t* my_buf, int& nstore, int lane,
-                                              uint64_t* acc_empty_local, uint32_t acc_empty_remote,
-                                              const FixUp* fx = nullptr) {
+// BETA (plain epilogue only): compiled for beta != 0, where C is prefetched a chunk ahead, or for beta == 0, where
+// the tensor-memory read is started early instead; the two never hold their look-ahead registers at the same time.
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int NBUF, bool RELEASE, int MODE, bool BETA>
+__device__ __forceinline__ void epilogue_tile_impl(const GemmArgs& g, const CUtensorMap* tmD, uint32_t t_addr, int m0,
+                                                   int n0, uint8_t* my_buf, int& nstore, int lane,
+                                                   uint64_t* acc_empty_local, uint32_t acc_empty_remote,
+                                                   const FixUp* fx) {
   constexpr int EPI_BUF = 4096;
   constexpr bool INT_OUT = (KIND == KIND_I8);
   // columns handled per TMA store: a 128-byte row for N-major output, 32 for M-major
@@ -176,11 +178,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
     }
   };
   request_others(0);
+  // beta != 0: the 32 values of C a thread needs for a chunk are requested one chunk ahead, so that their way from
+  // memory overlaps the tensor-memory read and the stores of the chunk before (the tensor cores wait for this loop)
+  constexpr bool CPRE = MODE == EPI_PLAIN && BETA;
+  uint32_t cpre[CPRE ? 32 : 1];
+  auto request_c = [&](int q) {
+    if constexpr (CPRE) {
+      const int row = m0 + lane;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = n0 + q * 32 + j;
+        cpre[j] = 0u;
+        if (row < g.M && col < g.N) {
+          const long long off = (long long)row * g.c_sm + (long long)col * g.c_sn;
+          if constexpr (INT_OUT) cpre[j] = (uint32_t)reinterpret_cast<const int*>(g.C)[off];
+          else cpre[j] = __float_as_uint(load_c_as_float<OutT>(g.C, off));
+        }
+      }
+    }
+  };
+  request_c(0);
 #pragma unroll 1
   for (int c = 0; c < BN / SC; ++c) {
     uint8_t* sb = my_buf + (nstore % NBUF) * EPI_BUF;
     // plain epilogue: the tensor-memory read of this chunk is in flight while the warp waits for its staging buffer
-    constexpr bool EARLY_LD = MODE == EPI_PLAIN;
+    constexpr bool EARLY_LD = MODE == EPI_PLAIN && !BETA;
     uint32_t v0[EARLY_LD ? 32 : 1];
     if constexpr (EARLY_LD) tmem_ld_x32(t_addr + c * SC, v0);
     if (lane == 0) tma_store_wait_read<NBUF - 1>();  // the store that last used `sb` has drained
@@ -209,7 +231,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
         }
         if (q + 1 < BN / 32) request_others(q + 1);
       } else if constexpr (!RED) {
-        if (s == 0) {
+        if (EARLY_LD && s == 0) {
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = v0[j];
@@ -227,7 +249,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
           else mbar_arrive(acc_empty_local);
         }
       }
-      if (!RED && g.beta != 0.f) {
+      if constexpr (CPRE) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if constexpr (INT_OUT) v[j] = (uint32_t)((int)v[j] + (int)cpre[j]);
+          else v[j] = __float_as_uint(__uint_as_float(v[j]) * g.alpha + g.beta * __uint_as_float(cpre[j]));
+        }
+        if (c * SUB + s + 1 < BN / 32) request_c(c * SUB + s + 1);
+      } else if (MODE == EPI_SUM && g.beta != 0.f) {
         const int row = m0 + lane;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -317,6 +346,24 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorM
       tma_store_commit();
     }
     ++nstore;
+  }
+}
+
+template <int KIND, typename OutT, bool OUT_M_MAJOR, int BN, int NBUF = 2, bool RELEASE = true, int MODE = EPI_PLAIN>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const CUtensorMap* tmD, uint32_t t_addr, int m0,
+                                              int n0, uint8_t* my_buf, int& nstore, int lane,
+                                              uint64_t* acc_empty_local, uint32_t acc_empty_remote,
+                                              const FixUp* fx = nullptr) {
+  if constexpr (MODE == EPI_PLAIN) {
+    if (g.beta != 0.f)
+      epilogue_tile_impl<KIND, OutT, OUT_M_MAJOR, BN, NBUF, RELEASE, MODE, true>(g, tmD, t_addr, m0, n0, my_buf, nstore, lane,
+                                                                                  acc_empty_local, acc_empty_remote, fx);
+    else
+      epilogue_tile_impl<KIND, OutT, OUT_M_MAJOR, BN, NBUF, RELEASE, MODE, false>(g, tmD, t_addr, m0, n0, my_buf, nstore, lane,
+                                                                                   acc_empty_local, acc_empty_remote, fx);
+  } else {
+    epilogue_tile_impl<KIND, OutT, OUT_M_MAJOR, BN, NBUF, RELEASE, MODE, false>(g, tmD, t_addr, m0, n0, my_buf, nstore, lane,
+                                                                                 acc_empty_local, acc_empty_remote, fx);
   }
 }
 
