@@ -22,6 +22,8 @@
  *     the ldmatrix copy) are ordered by the library with an event whenever two of them that share a scratch
  *     buffer come on different streams; everything else runs concurrently.  Scratch buffers are allocated once,
  *     on first use, at their final size; only the Float32 split buffer grows with the operands.
+ *   - Environment: MOYE_B200_LOG=1 prints one line per product / copy on stderr with the kernel the dispatch
+ *     chose; =2 also prints every error message as it is set.  Launching entry points open an NVTX range.
  */
 #ifndef MOYE_B200_H
 #define MOYE_B200_H

@@ -2,7 +2,10 @@
 // construction.  Argument checking lives here and in the per-kernel launchers: a request the
 // kernels cannot serve is an error, never a slower fallback.
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "common.h"
 #include "ptx.cuh"
@@ -11,12 +14,34 @@ namespace moye {
 
 static thread_local char g_err[512] = "";
 
+int log_level() {
+  static const int level = [] {
+    const char* e = std::getenv("MOYE_B200_LOG");
+    return e ? std::atoi(e) : 0;
+  }();
+  return level;
+}
+
+void log_line(const char* fmt, ...) {
+  if (log_level() < 1) return;
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "[moye_b200] %s\n", buf);
+}
+
 void set_error(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+  if (log_level() >= 2) fprintf(stderr, "[moye_b200] error: %s\n", g_err);
 }
+
+NvtxRange::NvtxRange(const char* name) { nvtxRangePushA(name); }
+NvtxRange::~NvtxRange() { nvtxRangePop(); }
 const char* get_error() { return g_err; }
 
 // cuTensorMapEncodeTiled is fetched through the runtime so the library has no link-time
@@ -272,6 +297,7 @@ int moye_b200_selftest_dirty_tickets(moye_handle_t h, void* stream) {
 
 int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t* A, const moye_tensor_t* B,
                    const moye_tensor_t* C, const moye_gemm_params_t* params, void* stream) {
+  NvtxRange range("moye_b200_gemm");
   if (int rc = check_handle(h)) return rc;
   if (!D || !A || !B) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "D, A and B must be non-null");
   return launch_gemm(h, D, A, B, C, params, static_cast<cudaStream_t>(stream));
@@ -279,12 +305,14 @@ int moye_b200_gemm(moye_handle_t h, const moye_tensor_t* D, const moye_tensor_t*
 
 int moye_b200_copy(moye_handle_t h, const moye_tensor_t* dst, const moye_tensor_t* src,
                    const moye_copy_params_t* params, void* stream) {
+  NvtxRange range("moye_b200_copy");
   if (int rc = check_handle(h)) return rc;
   if (!dst || !src) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "dst and src must be non-null");
   return launch_copy(h, dst, src, params, static_cast<cudaStream_t>(stream));
 }
 
 int moye_b200_axpby(moye_handle_t h, const moye_tensor_t* Y, const moye_tensor_t* X, float a, float b, void* stream) {
+  NvtxRange range("moye_b200_axpby");
   if (int rc = check_handle(h)) return rc;
   if (!Y || !X) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "Y and X must be non-null");
   return launch_axpby(h, Y, X, a, b, static_cast<cudaStream_t>(stream));
@@ -292,6 +320,7 @@ int moye_b200_axpby(moye_handle_t h, const moye_tensor_t* Y, const moye_tensor_t
 
 int moye_b200_layout_copy(moye_handle_t h, void* dst, const moye_layout_t* dl, const void* src,
                           const moye_layout_t* sl, int32_t elem_bytes, void* stream) {
+  NvtxRange range("moye_b200_layout_copy");
   if (int rc = check_handle(h)) return rc;
   if (!dst || !src || !dl || !sl) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "null argument");
   return launch_layout_copy(h, dst, dl, src, sl, elem_bytes, static_cast<cudaStream_t>(stream));
@@ -299,6 +328,7 @@ int moye_b200_layout_copy(moye_handle_t h, void* dst, const moye_layout_t* dl, c
 
 int moye_b200_layout_eval(moye_handle_t h, const moye_layout_t* l, int64_t first, int64_t n, int64_t* out,
                           void* stream) {
+  NvtxRange range("moye_b200_layout_eval");
   if (int rc = check_handle(h)) return rc;
   if (!l || (!out && n > 0)) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "null argument");
   return launch_layout_eval(h, l, first, n, out, static_cast<cudaStream_t>(stream));

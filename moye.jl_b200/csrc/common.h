@@ -17,6 +17,16 @@ namespace moye {
 
 void set_error(const char* fmt, ...);
 const char* get_error();
+// MOYE_B200_LOG=1: one line per entry-point call on stderr (shape, types, the kernel and tile chosen);
+// MOYE_B200_LOG=2: also every error message as it is set.  Read once per process.
+int log_level();
+void log_line(const char* fmt, ...);
+
+// NVTX range around an entry point (shows up in Nsight timelines); a no-op costing one branch when no tool is attached.
+struct NvtxRange {
+  explicit NvtxRange(const char* name);
+  ~NvtxRange();
+};
 
 #define MOYE_FAIL(code, ...)     \
   do {                           \

@@ -180,6 +180,7 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst_in, const moye_tensor
   const bool d0 = dst->stride[0] == 1 || m == 1, d1 = dst->stride[1] == 1 || n == 1;
   if (p.mode == MOYE_COPY_TRANSPOSE || (p.mode == MOYE_COPY_AUTO && !(s0 && d0) && ((s1 && d0) || (s0 && d1)))) {
     if (p.tile_m != 0 || p.tile_n != 0) MOYE_FAIL(MOYE_ERR_INVALID_ARG, "the transposing copy chooses its own tiles");
+    log_line("copy %lld x %lld, %d-byte elements -> transposing kernel", (long long)m, (long long)n, eb);
     if (src->stride[1] == 1 && dst->stride[0] == 1)
       return launch_transpose(h, dst->ptr, dst->stride[1], src->ptr, src->stride[0], src->dtype, m, n, stream);
     if (src->stride[0] == 1 && dst->stride[1] == 1)  // the mirrored case: swap the modes of both views
@@ -200,6 +201,8 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst_in, const moye_tensor
     MOYE_FAIL(MOYE_ERR_MISALIGNED, "column length and pitches must be multiples of 16 bytes for 128-bit atoms");
   int mode = p.mode;
   if (mode == MOYE_COPY_AUTO) mode = (eb <= 8 && tile_m <= 256) ? MOYE_COPY_TMA : MOYE_COPY_UNIVERSAL128;
+  log_line("copy %lld x %lld, %d-byte elements, tile %d x %d -> %s", (long long)m, (long long)n, eb, tile_m, tile_n,
+           mode == MOYE_COPY_TMA ? "TMA ring" : "128-bit universal copy");
 
   if (mode == MOYE_COPY_UNIVERSAL128) {
     const long long tile_m_bytes = (long long)tile_m * eb;

@@ -218,7 +218,10 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     use_skinny = (M <= 16 && nk >= (64ll << 20)) || (M <= 16 && tiles <= 64 && K >= 1024 && nk >= (8ll << 20)) ||
                  (M <= 4 && nk >= (8ll << 20));
   }
-  if (use_skinny) return launch_gemm_skinny(h, D, A, B, &p, stream);
+  if (use_skinny) {
+    log_line("gemm %lld x %lld x %lld  in %d  -> stream-K decode kernel", (long long)M, (long long)N, (long long)K, A->dtype);
+    return launch_gemm_skinny(h, D, A, B, &p, stream);
+  }
 
   int bn = p.tile_n;
   if (bn == 0) {
@@ -405,6 +408,12 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     a.sk_ws = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(h->tail_ws) + kTailTicketBytes);
   }
 
+  if (log_level() >= 1)
+    log_line("gemm %lld x %lld x %lld  in %d out %d  A %s B %s D %s  -> %s, tile_n %d%s%s", (long long)M, (long long)N, (long long)K,
+             A->dtype, out, a_mn ? "MN-major" : "K-major", b_mn ? "MN-major" : "K-major", m_major ? "M-major" : "N-major",
+             split ? "split-K clusters" : (wide ? "CTA pairs, 256 x 512 tiles" : (pair ? "CTA pairs" : "single CTAs")), wide ? 512 : bn,
+             split ? (split == 2 ? ", 2 CTAs per tile" : (split == 4 ? ", 4 CTAs per tile" : ", 8 CTAs per tile")) : "",
+             a.sk_tiles > 0 ? ", K-split tail" : "");
   if (split) return launch_dense_splitk(kind, out, bn, h, ta, tb, a, split, stream);
   if (wide) return launch_dense_wide(kind, out, m_major, h, ta, tb, td, a, stream);
   if (pair) return launch_dense_pair(kind, out, m_major, bn, h, ta, tb, td, a, stream);

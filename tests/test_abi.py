@@ -85,3 +85,16 @@ def test_forbidden_copy_qualifier_is_absent():
                     assert token not in open(os.path.join(dirpath, f), errors="ignore").read(), f
     for f in ("bench.py", "__graft_entry__.py"):
         assert token not in open(os.path.join(ROOT, f)).read()
+
+
+def test_log_environment_variable_reports_errors_on_stderr():
+    """MOYE_B200_LOG=2: every error message goes to stderr as it is set; unset: silence.  (Level 1 also prints one
+    line per entry-point call with the kernel chosen; that needs a device and is covered by the GPU tests.)"""
+    import sys
+    script = ("import ctypes, sys; sys.path.insert(0, %r); import __graft_entry__ as g; lib = g.load_package()._lib.load(); "
+              "assert lib.moye_b200_gemm(None, None, None, None, None, None, None) == -1" % ROOT)
+    loud = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=dict(os.environ, MOYE_B200_LOG="2"))
+    assert loud.returncode == 0 and "[moye_b200] error: null handle" in loud.stderr
+    env = {k: v for k, v in os.environ.items() if k != "MOYE_B200_LOG"}
+    quiet = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env)
+    assert quiet.returncode == 0 and "[moye_b200]" not in quiet.stderr

@@ -696,3 +696,35 @@ def test_parity_under_the_debug_build(dev):
     assert "libmoye_b200_debug.so" in subprocess.run(
         [sys.executable, "-c", "import __graft_entry__ as g; print(g.load_package()._lib.LIB_PATH)"], capture_output=True,
         text=True, env=env, cwd=root).stdout
+
+
+_LOG_SCRIPT = r"""
+import sys
+import torch
+sys.path.insert(0, sys.argv[1])
+import __graft_entry__ as ge
+mb = ge.load_package()
+dev = torch.device("cuda", 0)
+for M, N, K in ((512, 1024, 256), (16, 2048, 1024)):
+    A = torch.randn(M, K, device=dev).bfloat16(); B = torch.randn(N, K, device=dev).bfloat16()
+    D = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    mb.matmul(A, B, D)
+src = torch.randn(256, 512, device=dev)
+dst = torch.empty(512, 256, device=dev).t()
+mb.copyto_(mb.MoYeArray(dst), mb.MoYeArray(src))
+mb.synchronize_status(dev)
+"""
+
+
+def test_log_level_one_names_the_kernel_chosen(dev):
+    """MOYE_B200_LOG=1: one line per call on stderr with the shape and the kernel / tile the dispatch chose."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", _LOG_SCRIPT, root], capture_output=True, text=True,
+                         env=dict(os.environ, MOYE_B200_LOG="1"), timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stderr.splitlines() if l.startswith("[moye_b200]")]
+    assert any("gemm 512 x 1024 x 256" in l and "tile_n" in l for l in lines), lines
+    assert any("gemm 16 x 2048 x 1024" in l for l in lines), lines
+    assert any(l.startswith("[moye_b200] copy") for l in lines), lines
