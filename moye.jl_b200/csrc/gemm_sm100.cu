@@ -408,6 +408,11 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     a.sk_ws = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(h->tail_ws) + kTailTicketBytes);
   }
 
+  if (split) {  // the partial tiles of a cluster meet in the same scratch
+    if (int rc = ensure_tail_workspace(h)) return rc;
+    a.sk_ws = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(h->tail_ws) + kTailTicketBytes);
+  }
+
   if (log_level() >= 1)
     log_line("gemm %lld x %lld x %lld  in %d out %d  A %s B %s D %s  -> %s, tile_n %d%s%s", (long long)M, (long long)N, (long long)K,
              A->dtype, out, a_mn ? "MN-major" : "K-major", b_mn ? "MN-major" : "K-major", m_major ? "M-major" : "N-major",

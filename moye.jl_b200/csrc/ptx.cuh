@@ -126,6 +126,13 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const vo
 }
 // Orders this thread's earlier and later accesses across the generic and the async proxy, all state spaces.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, `bytes` a multiple of 16.
+// Completion is counted on `mbar` (complete_tx), like a tensor load.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(mbar))
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -243,6 +250,16 @@ __device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+// 128-bit store into the shared memory of any CTA of the cluster.
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// Programmatic dependent launch.  `griddep_wait` returns once the grids this one depends on have completed and
+// their writes are visible (at once when the launch carried no such dependency); nothing before it may touch global
+// memory another grid writes.  `griddep_launch` lets the next grid of the stream, if it was launched with the
+// programmatic attribute, begin its own set-up while this one finishes.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // TMA load whose completion is counted on an mbarrier of the CTA pair's leader (`mbar_cluster_addr`
