@@ -18,12 +18,14 @@
  *     otherwise; `moye_b200_last_error()` gives a thread-local message.  Nothing aborts,
  *     traps or throws across this boundary, and there is no CPU fallback.
  *   - One handle per (host thread, device).  A handle may be used with several streams: the kernels that keep
- *     scratch in the handle (the stream-K decode GEMM, the K-split tail of the dense kernel, the Float32 split,
- *     the ldmatrix copy) are ordered by the library with an event whenever two of them that share a scratch
+ *     scratch in the handle (the stream-K decode GEMM, the K-split tail of the dense kernel and the split-K cluster
+ *     kernel, the Float32 split, the ldmatrix copy) are ordered by the library with an event whenever two of them that share a scratch
  *     buffer come on different streams; everything else runs concurrently.  Scratch buffers are allocated once,
  *     on first use, at their final size; only the Float32 split buffer grows with the operands.
  *   - Environment: MOYE_B200_LOG=1 prints one line per product / copy on stderr with the kernel the dispatch
  *     chose; =2 also prints every error message as it is set.  Launching entry points open an NVTX range.
+ *     MOYE_B200_NO_PDL=1 launches the split-K kernel without the programmatic dependent-launch attribute (for
+ *     profilers that do not list kernels launched with it).
  */
 #ifndef MOYE_B200_H
 #define MOYE_B200_H
@@ -127,8 +129,9 @@ typedef struct {
   int32_t path;                  /* 0 auto, 1 dense kernel (single CTAs), 2 skinny stream-K kernel (M <= 128),
                                     3 dense kernel on CTA pairs (cta_group::2), 256 x tile_n tiles,
                                     4 CTA pairs on 256 x 512 tiles,
-                                    5 split-K on thread-block clusters: 128 x tile_n tiles, `split_k` CTAs per tile
-                                    reduce through distributed shared memory (for outputs with few tiles) */
+                                    5 split-K on thread-block clusters: 128 x tile_n tiles, the `split_k` CTAs of a tile
+                                    sum their parts through the handle's scratch (for outputs with few tiles; at most
+                                    591 CTAs with tile_n 256, else MOYE_ERR_TOO_LARGE) */
   int32_t flags;                 /* fused epilogue: MOYE_EPI_* activation | MOYE_EPI_BIAS_*; 0 = plain GEMM */
   const float* bias;             /* device pointer, fp32, read only when a bias mode is set */
 } moye_gemm_params_t;

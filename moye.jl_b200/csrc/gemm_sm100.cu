@@ -203,20 +203,17 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   }
 
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
-  // Automatic choice for decode shapes, from measurements at M = 1 .. 128 (bf16, weights from 2048 x 8192 to
-  // 28672 x 8192).  The dense kernel on single CTAs streams one tile per CTA over the whole of K, so it is only as
-  // fast as its row of tiles is wide.  The stream-K kernel deals equal runs of (row-block, K-block) units to all
-  // SMs; it is the fastest form up to 16 rows (X tiles of 2 KB): on the largest weights (16 x 28672 x 8192: 77 us
-  // against 81-86), wherever the row of tiles is short, and with very few rows (M = 1 at 28672 x 8192: 75 against
-  // 99).  From 17 rows its X tiles and its epilogue grow with M and the split-K kernel (below) or the dense
-  // kernel take over (4096 x 4096 weights, M = 64: 16.6 us split-K, 25 stream-K, 25 dense).
+  // Automatic choice for decode shapes, from measurements at M = 1 .. 128 (bf16, weights from 1024 x 4096 to
+  // 28672 x 8192).  The stream-K kernel deals equal runs of (row-block, K-block) units to all SMs; it is the fastest
+  // form on large weights, where the other kernels' tile counts do not divide the SMs (16 x 28672 x 8192: 77-79 us
+  // against 93 for split-K on clusters and 85 for single CTAs; 8192 x 8192 and 14336 x 4096 weights with 1-4 rows:
+  // 30.4 / 28.6 us against 31.1 / 29.7).  On mid-sized weights the cluster split-K kernel (below) is faster at every M
+  // (4096 x 4096: 12.5-14.0 us against 16.6-17.1; 8192 x 2048: 13.8 against 16.5-17; 2048 x 8192: 15.9-16.3 against
+  // 16.5-18.6; 4096 x 1024: 8.9 against 12.4), and from 17 rows the stream-K kernel's X tiles and epilogue grow with M.
   bool use_skinny = p.path == 2;
   if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && !a_mn && !b_mn && N >= 128 && K >= 512) {
     const long long nk = (long long)N * K;
-    const long long tiles256 = (N + 255) / 256;
-    const long long tiles = tiles256 >= (long long)h->num_sms * 2 / 3 ? tiles256 : (N + 127) / 128;
-    use_skinny = (M <= 16 && nk >= (64ll << 20)) || (M <= 16 && tiles <= 64 && K >= 1024 && nk >= (8ll << 20)) ||
-                 (M <= 4 && nk >= (8ll << 20));
+    use_skinny = nk >= (64ll << 20) || (M <= 4 && nk >= (48ll << 20));
   }
   if (use_skinny) {
     log_line("gemm %lld x %lld x %lld  in %d  -> stream-K decode kernel", (long long)M, (long long)N, (long long)K, A->dtype);
@@ -293,9 +290,9 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   // path 5 = split-K on clusters (128 x tile_n tiles, `split_k` CTAs per tile).  Chosen automatically when the
   // output has so few tiles that the other kernels would leave most SMs idle and K is long enough to cut (at least
   // 8 blocks per CTA): the tile width (256, 128) and split (4, 2) that put the most CTAs on the SMs without
-  // exceeding them (4096 x 4096 weights, M = 128: 16.7 us with 32 tiles x 4 against 25-27 unsplit; M = 512: 27
-  // against 31).  Clusters of 8 measured slower than clusters of 4 with the same number of CTAs and are only used
-  // on request.
+  // exceeding them (4096 x 4096 weights, M = 128: 13.2 us with 32 tiles x 4 against 25-29 unsplit; M = 512: 22
+  // against 30).  Clusters of 8 measured slower than clusters of 4 with the same number of CTAs (4096 x 4096, M = 128:
+  // 24.2 us with 16 tiles x 8 against 13.2 with 32 x 4).
   const int kb_total = (int)((K + 128 / dtype_bytes(A->dtype) - 1) / (128 / dtype_bytes(A->dtype)));
   int split = 0;
   if (p.path == 5) {
@@ -322,6 +319,13 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
           break;
         }
       }
+    }
+    // clusters of 8 only where they put strictly more CTAs to work (128 x 1024 x 8192: 12.3 us with 8 tiles x 8
+    // against 16.0 with 8 x 4)
+    for (int bn_c = 256; bn_c >= 128; bn_c /= 2) {
+      if ((p.tile_n != 0 && bn_c != p.tile_n) || (bn_c == 256 && N <= 128) || (p.split_k != 0 && p.split_k != 8)) continue;
+      const long long tiles_c = ((M + 127) / 128) * ((N + bn_c - 1) / bn_c);
+      if (tiles_c * 8 <= h->num_sms && kb_total >= 64 && tiles_c * 8 > best_ctas) { best_ctas = tiles_c * 8; split = 8; bn = bn_c; }
     }
     if (p.path == 5 && split == 0) {  // asked for explicitly: honour it even where it is not the fast choice
       split = p.split_k ? p.split_k : 2;

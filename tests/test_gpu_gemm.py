@@ -605,6 +605,44 @@ def test_stream_k_on_two_streams_of_one_handle(mb, ho, dev):
         assert torch.equal(Y1[i], Y1[0]) and torch.equal(Y2[i], Y2[0])
 
 
+def test_split_k_clusters_share_scratch_across_streams_and_launches(mb, ho, dev):
+    """The cluster split-K kernel sums its partial tiles through the handle's scratch (shared with the K-split tail of
+    the 256 x 512 kernel) and is launched so that its set-up may overlap the previous grid.  Back-to-back launches on
+    one stream and alternating launches on two streams, mixed with products that take the tail, must all be right and
+    bit-equal from run to run; a request with more CTAs than the scratch has images is refused."""
+    M, N, K = 200, 2048, 2048
+    a, b, A, B, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
+    a2, b2, A2, B2, _ = operands(ho, "bf16", M, N, K, dev, (11, 12))
+    rows = np.arange(M, dtype=np.int32)
+    ref, ref2 = (ho.gemm_samples(x, w, dt, M, N, K, rows, threads=NTHREADS) for x, w in ((a, b), (a2, b2)))
+    Mt, Nt, Kt = 512, 1024, 1024
+    at, bt, At, Bt, dtt = operands(ho, "f16", Mt, Nt, Kt, dev, (3, 4))
+    reft = ho.gemm_samples(at, bt, dtt, Mt, Nt, Kt, np.arange(Mt, dtype=np.int32), threads=NTHREADS)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    torch.cuda.synchronize()
+    Y1 = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(8)]
+    Y2 = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(8)]
+    Ct = [torch.zeros(Mt, Nt, device=dev) for _ in range(4)]
+    for i in range(8):
+        mb.matmul(A, B, Y1[i], path=5, split_k=4 if i % 2 else 2, stream=ctypes.c_void_p(s1.cuda_stream))
+        mb.matmul(A2, B2, Y2[i], path=5, tile_n=128, stream=ctypes.c_void_p(s2.cuda_stream))
+        if i % 2:
+            mb.matmul(At, Bt, Ct[i // 2], path=4, tail=True, stream=ctypes.c_void_p(s1.cuda_stream))
+    torch.cuda.synchronize()
+    mb.synchronize_status(dev)
+    for i in range(8):
+        assert ho.max_rel_err(Y1[i].float().cpu().numpy(), ref) <= 1e-2, i
+        assert ho.max_rel_err(Y2[i].float().cpu().numpy(), ref2) <= 1e-2, i
+        assert torch.equal(Y1[i], Y1[i % 2]) and torch.equal(Y2[i], Y2[0])
+    for c in Ct:
+        assert ho.max_rel_err(c.cpu().numpy(), reft) <= 1e-2
+    big = torch.zeros(4096, 4096, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(mb.MoyeError) as e:
+        mb.matmul(big[:, :256], big[:, :256], torch.zeros(4096, 4096, dtype=torch.bfloat16, device=dev), path=5, split_k=8)
+    assert e.value.code == -9 and "image" in str(e.value)
+    mb.synchronize_status(dev)
+
+
 @pytest.mark.parametrize("M,N,K", [(4096, 4096, 4096), (1024, 8192, 8192), (300, 520, 1008), (2304, 1536, 768)])
 def test_stream_k_tail_equals_whole_tiles(mb, ho, dev, M, N, K):
     """The stream-K tail only changes who computes which K blocks: s8 results are identical to the whole-tile
