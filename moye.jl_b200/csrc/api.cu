@@ -22,6 +22,14 @@ int log_level() {
   return level;
 }
 
+bool launch_without_pdl() {
+  static const bool off = [] {
+    const char* e = std::getenv("MOYE_B200_NO_PDL");
+    return e && e[0] == '1';
+  }();
+  return off;
+}
+
 void log_line(const char* fmt, ...) {
   if (log_level() < 1) return;
   char buf[512];

@@ -22,6 +22,10 @@ const char* get_error();
 int log_level();
 void log_line(const char* fmt, ...);
 
+// MOYE_B200_NO_PDL=1: launch without the programmatic dependent-launch attribute (Nsight Compute does not list
+// kernels launched with it).  Read once per process.
+bool launch_without_pdl();
+
 // NVTX range around an entry point (shows up in Nsight timelines); a no-op costing one branch when no tool is attached.
 struct NvtxRange {
   explicit NvtxRange(const char* name);

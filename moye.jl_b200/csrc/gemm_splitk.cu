@@ -1,7 +1,5 @@
 #include "gemm_common.cuh"
 
-#include <cstdlib>
-
 namespace moye {
 
 // ------------------------------------------------------------------------------------------
@@ -327,9 +325,7 @@ static int launch_splitk_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUt
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  // MOYE_B200_NO_PDL=1 launches without that attribute: Nsight Compute does not list kernels launched with it
-  static const bool no_pdl = [] { const char* e = std::getenv("MOYE_B200_NO_PDL"); return e && e[0] == '1'; }();
-  cfg.numAttrs = no_pdl ? 1 : 2;
+  cfg.numAttrs = launch_without_pdl() ? 1 : 2;
   // a cluster of `split` CTAs, each with a whole SM's shared memory, must fit into one GPC: ask once per size
   for (; split >= 2; split /= 2) {
     attr[0].val.clusterDim.x = (unsigned)split;

@@ -173,6 +173,11 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __g
   cluster_arrive();
   cluster_wait();
   tc_fence_after_sync();
+  // Programmatic dependent launch: a pair that finds a free SM pair starts as soon as the CTAs of the stream's
+  // previous grid leave it and has its barriers and tensor memory ready when that grid completes; nothing above
+  // touches global memory, everything below comes after the wait.
+  griddep_launch();
+  griddep_wait();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
   if (warp == 0) {
@@ -390,13 +395,15 @@ static int launch_wide_cfg(moye_b200_ctx* h, const CUtensorMap& ta, const CUtens
   cfg.blockDim = dim3(320, 1, 1);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel waits for the previous grid itself
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = launch_without_pdl() ? 1 : 2;
   if (args.sk_tiles > 0) {  // the tail's scratch is shared by every launch of the handle
     if (int rc = order_scratch_use(h, &h->tail_order, stream)) return rc;
   }
