@@ -95,6 +95,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int grid = gridDim.x;
   const long long u_begin = run_start(blockIdx.x, g.units, grid);
   const long long u_end = run_start(blockIdx.x + 1, g.units, grid);
+  const int pre = u_end - u_begin < STAGES ? (int)(u_end - u_begin) : STAGES;
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -108,6 +109,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     fence_mbar_init();
     prefetch_tensormap(&tmW);
     prefetch_tensormap(&tmX);
+    // the first ring of loads is requested at once: it is in flight while warp 1 allocates tensor memory and the
+    // CTA meets at the barrier below
+    griddep_wait();
+    const uint64_t pol_w = l2_policy_evict_first();
+    const uint64_t pol_x = l2_policy_evict_last();
+    for (int i = 0; i < pre; ++i) {
+      const long long u = u_begin + i;
+      const int tile = (int)(u / g.k_blocks);
+      const int kb = (int)(u - (long long)tile * g.k_blocks);
+      mbar_arrive_expect_tx(&full[i], STAGE_BYTES);
+      uint8_t* sw = smem + i * STAGE_BYTES;
+      tma_load_2d_hint(sw, &tmW, &full[i], kb * BK, tile * 128, pol_w);
+      tma_load_2d_hint(sw + W_BYTES, &tmX, &full[i], kb * BK, 0, pol_x);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_holder, TMEM_COLS);
@@ -116,15 +131,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // programmatic dependent launch (handle-based launches carry the attribute; without it both are no-ops): the next
+  // grid of the stream may set itself up on this SM as soon as this CTA leaves; nothing above touched global memory
+  // except the loads behind the producer's own wait
+  griddep_launch();
+  griddep_wait();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
   if (warp == 0) {
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      int stage = 0;
-      uint32_t phase = 0;
-      for (long long u = u_begin; u < u_end; ++u) {
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (long long u = u_begin + pre; u < u_end; ++u) {
         const int tile = (int)(u / g.k_blocks);
         const int kb = (int)(u - (long long)tile * g.k_blocks);
         if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_SK_PROD)) break;
@@ -411,8 +431,17 @@ static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUt
   a.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(h->workspace) + kSkinnyTicketBytes);
   // every stream-K launch of a handle shares that scratch: a launch on another stream than the last one waits for it
   if (int rc = order_scratch_use(h, &h->sk_order, stream)) return rc;
-  kern<<<(int)grid, 192, SMEM, stream>>>(tw, tx, a);
-  MOYE_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel waits for the previous grid itself
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_without_pdl() ? 0 : 1;
+  MOYE_CUDA(cudaLaunchKernelEx(&cfg, kern, tw, tx, a));
   return scratch_used(&h->sk_order, stream);
 }
 
