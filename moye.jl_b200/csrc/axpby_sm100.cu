@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 
 #include "common.h"
+#include "ptx.cuh"
 
 namespace moye {
 
@@ -42,6 +43,8 @@ __global__ void __launch_bounds__(256)
 axpby_kernel(T* y, const T* x, long long rows, long long cols, long long pitch_y,
              long long pitch_x, float a, float b) {
   constexpr int VEC = 16 / (int)sizeof(T);
+  griddep_launch();  // programmatic dependent launch: see launch_dependent()
+  griddep_wait();
   const bool read_y = b != 0.f;
   const long long per_row = VECTOR ? cols / VEC : cols;
   const long long total = rows * per_row;
@@ -76,13 +79,13 @@ static int launch_axpby_t(moye_b200_ctx* h, void* y, const void* x, long long ro
   const long long cap = (long long)h->num_sms * 8;  // grid-stride beyond 8 CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
+  const dim3 g((unsigned)blocks), blk(256);
   if (vec)
-    axpby_kernel<T, true><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<T*>(y), static_cast<const T*>(x), rows, cols,
-                                                               pitch_y, pitch_x, a, b);
+    MOYE_CUDA(launch_dependent(axpby_kernel<T, true>, g, blk, 0, stream, static_cast<T*>(y), static_cast<const T*>(x), rows, cols,
+                               pitch_y, pitch_x, a, b));
   else
-    axpby_kernel<T, false><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<T*>(y), static_cast<const T*>(x), rows, cols,
-                                                                pitch_y, pitch_x, a, b);
-  MOYE_CUDA(cudaGetLastError());
+    MOYE_CUDA(launch_dependent(axpby_kernel<T, false>, g, blk, 0, stream, static_cast<T*>(y), static_cast<const T*>(x), rows, cols,
+                               pitch_y, pitch_x, a, b));
   return MOYE_OK;
 }
 

@@ -4,6 +4,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <utility>
+
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
@@ -25,6 +27,25 @@ void log_line(const char* fmt, ...);
 // MOYE_B200_NO_PDL=1: launch without the programmatic dependent-launch attribute (Nsight Compute does not list
 // kernels launched with it).  Read once per process.
 bool launch_without_pdl();
+
+// Launches `kern` with the programmatic dependent-launch attribute (unless MOYE_B200_NO_PDL=1): the grid may set
+// itself up while the stream's previous grid finishes.  Only for kernels that execute griddepcontrol.wait before
+// their first access to global memory.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_without_pdl() ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
 
 // NVTX range around an entry point (shows up in Nsight timelines); a no-op costing one branch when no tool is attached.
 struct NvtxRange {

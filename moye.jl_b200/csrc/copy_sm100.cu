@@ -54,6 +54,8 @@ struct CopyArgs {
 template <int ITEMS>
 __global__ void __launch_bounds__(256) copy_u128_kernel(const CopyArgs a) {
   extern __shared__ uint4 tile[];
+  griddep_launch();  // programmatic dependent launch: see launch_dependent()
+  griddep_wait();
   const int tmv = 1 << a.tmv_log2;
   const int tile_items = tmv * a.tn;
   for (long long t = blockIdx.x; t < a.tiles; t += gridDim.x) {
@@ -111,6 +113,8 @@ __global__ void __launch_bounds__(32) copy_tma_kernel(const __grid_constant__ CU
     prefetch_tensormap(&tmD);
   }
   __syncwarp();
+  griddep_launch();  // programmatic dependent launch: see launch_dependent()
+  griddep_wait();
   if (threadIdx.x == 0) {
     const long long first = blockIdx.x;
     const long long stride = gridDim.x;
@@ -226,11 +230,11 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst_in, const moye_tensor
     const int per_thread = (int)((items + 255) / 256);
     const size_t smem = (size_t)per_thread * 256 * 16;
     long long grid = a.tiles < (long long)h->num_sms * 8 ? a.tiles : (long long)h->num_sms * 8;
-    if (per_thread <= 1) copy_u128_kernel<1><<<(int)grid, 256, smem, stream>>>(a);
-    else if (per_thread <= 2) copy_u128_kernel<2><<<(int)grid, 256, smem, stream>>>(a);
-    else if (per_thread <= 4) copy_u128_kernel<4><<<(int)grid, 256, smem, stream>>>(a);
-    else copy_u128_kernel<8><<<(int)grid, 256, smem, stream>>>(a);
-    MOYE_CUDA(cudaGetLastError());
+    const dim3 g((unsigned)grid), b(256);
+    if (per_thread <= 1) MOYE_CUDA(launch_dependent(copy_u128_kernel<1>, g, b, smem, stream, a));
+    else if (per_thread <= 2) MOYE_CUDA(launch_dependent(copy_u128_kernel<2>, g, b, smem, stream, a));
+    else if (per_thread <= 4) MOYE_CUDA(launch_dependent(copy_u128_kernel<4>, g, b, smem, stream, a));
+    else MOYE_CUDA(launch_dependent(copy_u128_kernel<8>, g, b, smem, stream, a));
     return MOYE_OK;
   }
   if (mode == MOYE_COPY_TMA) {
@@ -264,8 +268,7 @@ int launch_copy(moye_b200_ctx* h, const moye_tensor_t* dst_in, const moye_tensor
     long long per_sm = (96 * 1024) / (tile_bytes * SLOTS);  // 2 CTAs per SM with 16 KB tiles, 4 with 8 KB ones
     per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
     long long grid = a.tiles < (long long)h->num_sms * per_sm ? a.tiles : (long long)h->num_sms * per_sm;
-    kern<<<(int)grid, 32, smem, stream>>>(ts, td, a);
-    MOYE_CUDA(cudaGetLastError());
+    MOYE_CUDA(launch_dependent(kern, dim3((unsigned)grid), dim3(32), smem, stream, ts, td, a));
     return MOYE_OK;
   }
   MOYE_FAIL(MOYE_ERR_INVALID_ARG, "unknown copy mode %d", mode);

@@ -72,6 +72,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_arrive();
   cluster_wait();  // both CTAs' barriers are initialised and both halves of the TMEM pair are allocated
   tc_fence_after_sync();
+  griddep_launch();  // programmatic dependent launch: nothing above touches global memory
+  griddep_wait();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
   if (warp == 0) {
@@ -207,13 +209,15 @@ static int launch_pair_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUten
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel waits for the previous grid itself
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = launch_without_pdl() ? 1 : 2;
   MOYE_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, td, args));
   return MOYE_OK;
 }

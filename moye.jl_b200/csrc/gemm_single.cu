@@ -66,6 +66,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  griddep_launch();  // programmatic dependent launch: see launch_dependent(); nothing above touches global memory
+  griddep_wait();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_holder);
 
   if (warp == 0) {
@@ -178,8 +180,7 @@ static int launch_inst(moye_b200_ctx* h, const CUtensorMap& ta, const CUtensorMa
   if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
   const int tiles = args.m_tiles * args.n_tiles;
   const int grid = tiles < h->num_sms ? tiles : h->num_sms;
-  kern<<<grid, 192, SMEM, stream>>>(ta, tb, td, args);
-  MOYE_CUDA(cudaGetLastError());
+  MOYE_CUDA(launch_dependent(kern, dim3((unsigned)grid), dim3(192), SMEM, stream, ta, tb, td, args));
   return MOYE_OK;
 }
 

@@ -101,6 +101,8 @@ __global__ void __launch_bounds__(64 * RM_) transpose_tma_kernel(const __grid_co
     prefetch_tensormap(&tmD);
   }
   __syncthreads();
+  griddep_launch();  // programmatic dependent launch: see launch_dependent()
+  griddep_wait();
 
   const long long first = blockIdx.x, stride = gridDim.x;
   const long long mine = first < a.tiles ? (a.tiles - first + stride - 1) / stride : 0;
@@ -188,8 +190,7 @@ static int launch_transpose_inst(moye_b200_ctx* h, const CUtensorMap& ts, const 
   if (per_sm > 4) per_sm = 4;
   if (per_sm < 1) per_sm = 1;
   long long grid = a.tiles < (long long)h->num_sms * per_sm ? a.tiles : (long long)h->num_sms * per_sm;
-  kern<<<(int)grid, 64 * RM_, Cfg::SMEM, stream>>>(ts, td, a);
-  MOYE_CUDA(cudaGetLastError());
+  MOYE_CUDA(launch_dependent(kern, dim3((unsigned)grid), dim3(64 * RM_), Cfg::SMEM, stream, ts, td, a));
   return MOYE_OK;
 }
 
