@@ -24,8 +24,8 @@
  *     on first use, at their final size; only the Float32 split buffer grows with the operands.
  *   - Environment: MOYE_B200_LOG=1 prints one line per product / copy on stderr with the kernel the dispatch
  *     chose; =2 also prints every error message as it is set.  Launching entry points open an NVTX range.
- *     MOYE_B200_NO_PDL=1 launches every kernel without the programmatic dependent-launch attribute (for
- *     profilers that do not list kernels launched with it).
+ *     MOYE_B200_NO_PDL=1 launches every kernel without the programmatic dependent-launch attribute (to compare
+ *     with and without).
  */
 #ifndef MOYE_B200_H
 #define MOYE_B200_H

@@ -24,8 +24,8 @@ const char* get_error();
 int log_level();
 void log_line(const char* fmt, ...);
 
-// MOYE_B200_NO_PDL=1: launch without the programmatic dependent-launch attribute (Nsight Compute does not list
-// kernels launched with it).  Read once per process.
+// MOYE_B200_NO_PDL=1: launch without the programmatic dependent-launch attribute (to compare with and without).
+// Read once per process.
 bool launch_without_pdl();
 
 // Launches `kern` with the programmatic dependent-launch attribute (unless MOYE_B200_NO_PDL=1): the grid may set
