@@ -719,10 +719,61 @@ def extras(mb, torch, dev, peaks):
             out[name] = {"ms": ms, "TFLOP/s": 2.0 * M * N * K / ms / 1e9}
         del sets, plans
         torch.cuda.empty_cache()
+    out["library_same_box"] = library_rates(torch, dev, out)
     out["copy_f16_8192"] = copy_rates(mb, torch, dev, peaks, 20, 5)
     out["transpose_8192"] = transpose_rates(mb, torch, dev, peaks, 20, 5)
     mb.synchronize_status(dev)
     return out
+
+
+def library_rates(torch, dev, ours):
+    """The vendor library (cuBLAS / cuBLASLt through torch) on the same box, same shapes and same data distributions, timed the
+    same way: a yardstick for the kinds that have no driver-measured peak (8-bit), never part of `value`.  `ratio` = ours / library."""
+    res = {}
+    stream = torch.cuda.current_stream()
+
+    def run(name, fn, flops):
+        try:
+            ms = time_launches(torch, fn, 10, 3, stream)
+        except Exception as e:  # a kind this torch build has no library kernel for
+            res[name] = {"unavailable": str(e).splitlines()[0][:120]}
+            return
+        res[name] = {"ms": ms, "TFLOP/s": flops / ms / 1e9}
+        if name in ours and "ms" in ours[name]:
+            res[name]["ratio"] = ms / ours[name]["ms"]
+
+    for name in ("gemm_f16_4096", "gemm_bf16_8192", "gemm_s8_16384x8192x8192", "gemm_e4m3_16384x8192x8192", "decode_bf16_16x28672x8192",
+                 "gemm_bf16_256x4096x4096"):
+        kind, M, N, K, o = WORKLOADS[name]
+        nset = 3 if M <= 32 else (12 if M <= 512 else 1)
+        sets = [make_operands(torch, kind, M, N, K, o, dev, seed=40 + i) for i in range(nset)]
+        i = [0]
+        if kind in ("f16", "bf16"):
+            outs = [torch.empty(M, N, device=dev, dtype=a.dtype) for a, _, _ in sets]
+
+            def fn():
+                i[0] += 1
+                a, b, _ = sets[i[0] % nset]
+                torch.matmul(a, b.t(), out=outs[i[0] % nset])
+        elif kind == "s8":
+            def fn():
+                i[0] += 1
+                a, b, _ = sets[i[0] % nset]
+                torch._int_mm(a, b.t())
+        else:
+            sa = torch.tensor(0.05, device=dev)
+            sb = torch.tensor(0.02, device=dev)
+
+            def fn():
+                i[0] += 1
+                a, b, _ = sets[i[0] % nset]
+                torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        run(name, fn, 2.0 * M * N * K)
+        del sets
+        torch.cuda.empty_cache()
+    res["note"] = ("torch.matmul / torch._int_mm / torch._scaled_mm; 16-bit library outputs are 16-bit where ours are fp32 for the "
+                   "f16 / bf16 dense workloads (less output traffic for the library)")
+    return res
 
 
 def copy_rates(mb, torch, dev, peaks, steps, warmup):
