@@ -241,19 +241,6 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
-// 128-bit load from the shared memory of any CTA of the cluster (address from mapa_shared).
-__device__ __forceinline__ uint4 ld_shared_cluster_v4(uint32_t cluster_addr) {
-  uint4 v;
-  asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(cluster_addr)
-               : "memory");
-  return v;
-}
-// 128-bit store into the shared memory of any CTA of the cluster.
-__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 // Programmatic dependent launch.  `griddep_wait` returns once the grids this one depends on have completed and
 // their writes are visible (at once when the launch carried no such dependency); nothing before it may touch global
 // memory another grid writes.  `griddep_launch` lets the next grid of the stream, if it was launched with the
