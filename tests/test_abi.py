@@ -98,3 +98,26 @@ def test_log_environment_variable_reports_errors_on_stderr():
     env = {k: v for k, v in os.environ.items() if k != "MOYE_B200_LOG"}
     quiet = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env)
     assert quiet.returncode == 0 and "[moye_b200]" not in quiet.stderr
+
+
+def build_c_abi_smoke(tmp_path):
+    """Compiles tests/c_abi_smoke.cpp against the header and the in-tree library with g++ (no nvcc, no Python)."""
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    libdir = os.path.join(ROOT, "moye.jl_b200", "lib")
+    exe = tmp_path / "c_abi_smoke"
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+                    os.path.join(ROOT, "tests", "c_abi_smoke.cpp"), "-o", str(exe), "-L", libdir, "-lmoye_b200",
+                    "-L", os.path.join(cuda, "lib64"), "-lcudart", f"-Wl,-rpath,{libdir}",
+                    f"-Wl,-rpath,{os.path.join(cuda, 'lib64')}"], check=True)
+    return str(exe)
+
+
+def test_cpp_caller_links_and_reports_no_device(mb, tmp_path):
+    """A C++ program that uses only include/moye_b200.h and the shared library builds and links; without a device it
+    gets MOYE_ERR_NO_DEVICE from moye_b200_create (exit code 3), not a crash and not a CPU result."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present: the GPU test runs the same program to the end")
+    mb._lib.load()
+    res = subprocess.run([build_c_abi_smoke(tmp_path)], capture_output=True, text=True)
+    assert res.returncode == 3 and "no CPU path" in res.stdout, res.stdout + res.stderr

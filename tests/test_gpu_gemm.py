@@ -766,3 +766,12 @@ def test_log_level_one_names_the_kernel_chosen(dev):
     assert any("gemm 512 x 1024 x 256" in l and "tile_n" in l for l in lines), lines
     assert any("gemm 16 x 2048 x 1024" in l for l in lines), lines
     assert any(l.startswith("[moye_b200] copy") for l in lines), lines
+
+
+def test_cpp_caller_through_the_c_abi(dev, tmp_path):
+    """tests/c_abi_smoke.cpp -- a C++ caller with the header, the CUDA runtime and the library, nothing else: an exact
+    integer-valued fp16 product on ragged sizes, its transposing copy, the status call, and a refused operand."""
+    import subprocess
+    from test_abi import build_c_abi_smoke
+    res = subprocess.run([build_c_abi_smoke(tmp_path)], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "C_ABI_SMOKE_OK" in res.stdout, res.stdout + res.stderr
