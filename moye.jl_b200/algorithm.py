@@ -17,8 +17,8 @@ import torch
 
 from . import _lib
 from .array import MoYeArray, isgmem
-from .atom import DTYPE_BITS, TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
-from .layout import Layout, coalesce, size
+from .atom import TiledCopy, TiledMMA, make_tiled_mma, sm100_mma_op
+from .layout import coalesce, size
 
 __all__ = ["copyto_", "copy_dispatch", "gemm_", "matmul", "layout_eval", "synchronize_status", "current_stream_ptr",
            "gemm_skinny_static_", "gemm_skinny_static_status", "plan_gemm", "plan_copy", "LaunchPlan", "axpby_"]

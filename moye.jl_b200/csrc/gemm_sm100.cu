@@ -249,7 +249,7 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
     tp.last_wave = kb_all;
     if ((p.flags & MOYE_GEMM_TAIL_OFF) || kb_all < 2) return tp;
     const long long chains = pairs - rest < rest ? pairs - rest : rest;
-    const long long base = rest / chains, len_max = base + (rest % chains ? 1 : 0);
+    const long long base = rest / chains;
     const long long lead = kTailLead < kb_all / 4 ? kTailLead : kb_all / 4;
     // every head h(i) = (i+1) t - i kb - lead and every tail must keep at least one K block
     auto busy = [&](long long len) { return (len * kb_all + lead + len) / (len + 1); };  // ceil((len kb + lead) / (len + 1))

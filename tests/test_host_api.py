@@ -4,7 +4,6 @@ TiledCopy / TiledMMA partitioning (reference test/copy.jl:102-145, test/tiled_mm
 import json
 import os
 
-import numpy as np
 import pytest
 import torch
 

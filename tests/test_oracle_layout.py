@@ -1,7 +1,6 @@
 """Pins the layout-algebra oracle (oracle/layout_oracle.py) to the reference's own golden
 vectors.  Every case is transcribed from a test or docstring of MoYe.jl; the comment on each
 block gives the reference file and lines it comes from."""
-import itertools
 
 import pytest
 
