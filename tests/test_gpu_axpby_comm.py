@@ -67,6 +67,9 @@ def test_comm_entry_points_in_a_world_of_one(mb, ho, dev):
     ident = ctypes.create_string_buffer(128)
     rc = lib.moye_b200_comm_unique_id(ident)
     assert rc == 0, lib.moye_b200_last_error()
+    for bad_rank, bad_world in ((1, 1), (-1, 1), (0, 0)):                                       # a rank outside its world
+        assert lib.moye_b200_comm_init(h, bad_rank, bad_world, ident.raw) == -1 and b"bad rank" in lib.moye_b200_last_error()
+    assert lib.moye_b200_comm_init(None, 0, 1, ident.raw) == -1
     assert lib.moye_b200_comm_init(h, 0, 1, ident.raw) == 0, lib.moye_b200_last_error()
     try:
         assert lib.moye_b200_comm_init(h, 0, 1, ident.raw) == -1                                   # one communicator per handle
