@@ -10,6 +10,7 @@ using MoYe: MoYeArray, ViewEngine, Layout, TiledMMA, TiledCopy, AbstractMMAOP, A
             flatten, coalesce, shape, stride, layout, rank
 
 const libmoye_b200 = Ref{String}(get(ENV, "MOYE_B200_LIB", "libmoye_b200.so"))
+__init__() = atexit(destroy_handles)
 
 # ---- C structs (include/moye_b200.h)
 struct MoyeTensor
@@ -75,14 +76,24 @@ function moye_tensor(x::MoYeArray{T}) where {T}
                (Int64(shape(m1)), Int64(shape(m2)), 0, 0), (Int64(stride(m1)), Int64(stride(m2)), 0, 0))
 end
 
+const MOYE_B200_VERSION = 100   # MOYE_B200_VERSION of the header this file was written against
 const handles = Dict{Tuple{Int, Int}, Ptr{Cvoid}}()
 function handle()
     key = (Threads.threadid(), CUDA.deviceid(CUDA.device()))
     get!(handles, key) do
+        v = ccall((:moye_b200_version, libmoye_b200[]), Cint, ())
+        v == MOYE_B200_VERSION || error("libmoye_b200 is version $v, this binding expects $MOYE_B200_VERSION")
         h = Ref{Ptr{Cvoid}}(C_NULL)
         check(ccall((:moye_b200_create, libmoye_b200[]), Cint, (Ref{Ptr{Cvoid}},), h))
         h[]
     end
+end
+# one handle per (thread, device) for the life of the process; released at exit (scratch buffers, events, tensor-map cache)
+function destroy_handles()
+    for (_, h) in handles
+        ccall((:moye_b200_destroy, libmoye_b200[]), Cint, (Ptr{Cvoid},), h)
+    end
+    empty!(handles)
 end
 check(rc) = rc == 0 ? nothing :
     error("libmoye_b200 ($rc): " * unsafe_string(ccall((:moye_b200_last_error, libmoye_b200[]), Cstring, ())))
