@@ -771,6 +771,19 @@ def library_rates(torch, dev, ours):
         run(name, fn, 2.0 * M * N * K)
         del sets
         torch.cuda.empty_cache()
+    # Float32 operands, the element type of examples/gemm.jl (which checks itself against CUBLAS, :96): the library's fp32 GEMM
+    # (no tensor cores) beside our Float32-accurate three-product form, and its tf32 mode beside our single tf32 product
+    kind, M, N, K, o = WORKLOADS["gemm_f32_8192_colmajor"]
+    a, b, c = make_operands(torch, kind, M, N, K, o, dev, seed=50, colmajor=True)
+    was = torch.backends.cuda.matmul.allow_tf32
+    try:
+        for name, tf32 in (("gemm_f32_8192_colmajor", False), ("gemm_f32_8192_colmajor_tf32", True)):
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+            run(name, lambda: torch.matmul(a, b.t(), out=c), 2.0 * M * N * K)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = was
+    del a, b, c
+    torch.cuda.empty_cache()
     res["note"] = ("torch.matmul / torch._int_mm / torch._scaled_mm; 16-bit library outputs are 16-bit where ours are fp32 for the "
                    "f16 / bf16 dense workloads (less output traffic for the library)")
     return res
