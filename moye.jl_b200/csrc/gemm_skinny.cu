@@ -5,7 +5,12 @@
 //   - operands are swapped for the tensor core: 128 rows of W are the tcgen05 "M" side, the
 //     (zero-padded) rows of X the "N" side, so no MMA lanes are wasted on padding of W;
 //   - stream-K: the (W row-block, K-block) units are dealt out to one persistent CTA per SM in
-//     equal contiguous runs, so every SM streams the same number of bytes whatever N is;
+//     equal shares, so every SM streams the same number of bytes whatever N is.  With T row-blocks
+//     on G CTAs every CTA owns T div G whole row-blocks; the other T mod G row-blocks are cut along
+//     K into G equal contiguous runs.  A CTA works through its run of the cut row-blocks FIRST and
+//     its whole row-blocks last: the exchange of partial sums then overlaps the streaming of the
+//     whole row-blocks, and the kernel ends with a plain store (16 x 28672 x 8192: the tail after
+//     the last K block was 4.6 us with the cut row-blocks last);
 //   - a 12-deep TMA ring (about 200 KB of loads in flight per SM);
 //   - a CTA whose run covers only part of a row-block's K range writes an fp32 partial to a
 //     workspace; the CTA that arrives last at that row-block (an atomic ticket, no spinning)
@@ -24,7 +29,9 @@ namespace moye {
 struct SkinnyArgs {
   int M, N, K;
   int n_tiles, k_blocks;
-  long long units;      // n_tiles * k_blocks
+  int split_tiles;      // row-blocks 0 .. split_tiles-1 are cut along K and shared by all CTAs
+  int whole;            // whole row-blocks per CTA: split_tiles + c, split_tiles + c + grid, ...
+  long long units;      // split_tiles * k_blocks: the units of the cut row-blocks
   uint32_t idesc;
   float alpha;
   void* D;
@@ -93,9 +100,32 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int grid = gridDim.x;
+  // This CTA's work as one sequence v = 0 .. nv-1: first its run [u_begin, u_end) of the cut row-blocks' units, then
+  // its whole row-blocks.  A segment is a maximal stretch of one row-block: one accumulator.
+  const int kbn = g.k_blocks;
   const long long u_begin = run_start(blockIdx.x, g.units, grid);
   const long long u_end = run_start(blockIdx.x + 1, g.units, grid);
-  const int pre = u_end - u_begin < STAGES ? (int)(u_end - u_begin) : STAGES;
+  const int ns = (int)(u_end - u_begin);
+  const int nv = ns + g.whole * kbn;
+  auto locate = [&](int v, int& tile, int& kb) {
+    if (v < ns) {
+      const long long u = u_begin + v;
+      tile = (int)(u / kbn);
+      kb = (int)(u - (long long)tile * kbn);
+    } else {
+      const int j = (v - ns) / kbn;
+      tile = g.split_tiles + (int)blockIdx.x + j * grid;
+      kb = (v - ns) - j * kbn;
+    }
+  };
+  auto segment_end = [&](int v, int tile) {  // one past the last v of the segment that holds v
+    if (v < ns) {
+      const long long te = (long long)(tile + 1) * kbn - u_begin;
+      return te < ns ? (int)te : ns;
+    }
+    return ns + ((v - ns) / kbn + 1) * kbn;
+  };
+  const int pre = nv < STAGES ? nv : STAGES;
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -115,9 +145,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const uint64_t pol_w = l2_policy_evict_first();
     const uint64_t pol_x = l2_policy_evict_last();
     for (int i = 0; i < pre; ++i) {
-      const long long u = u_begin + i;
-      const int tile = (int)(u / g.k_blocks);
-      const int kb = (int)(u - (long long)tile * g.k_blocks);
+      int tile, kb;
+      locate(i, tile, kb);
       mbar_arrive_expect_tx(&full[i], STAGE_BYTES);
       uint8_t* sw = smem + i * STAGE_BYTES;
       tma_load_2d_hint(sw, &tmW, &full[i], kb * BK, tile * 128, pol_w);
@@ -144,9 +173,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const uint64_t pol_x = l2_policy_evict_last();
       int stage = pre == STAGES ? 0 : pre;
       uint32_t phase = pre == STAGES ? 1 : 0;
-      for (long long u = u_begin + pre; u < u_end; ++u) {
-        const int tile = (int)(u / g.k_blocks);
-        const int kb = (int)(u - (long long)tile * g.k_blocks);
+      for (int v = pre; v < nv; ++v) {
+        int tile, kb;
+        locate(v, tile, kb);
         if (!mbar_wait(&empty[stage], phase ^ 1, g.status, SITE_SK_PROD)) break;
         mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
         uint8_t* sw = smem + stage * STAGE_BYTES;
@@ -161,18 +190,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       uint32_t phase = 0;
       int seg = 0;
       bool ok = true;
-      long long u = u_begin;
-      while (u < u_end && ok) {
-        const int tile = (int)(u / g.k_blocks);
-        const long long tile_end = (long long)(tile + 1) * g.k_blocks;
-        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+      int v = 0;
+      while (v < nv && ok) {
+        int tile, kb_first;
+        locate(v, tile, kb_first);
+        const int seg_end = segment_end(v, tile);
         const int buf = seg & 1;
         const uint32_t aphase = (seg >> 1) & 1;
         if (!mbar_wait(&acc_empty[buf], aphase ^ 1, g.status, SITE_SK_ACC)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * NX;
         bool first = true;
-        for (; u < seg_end; ++u) {
+        for (; v < seg_end; ++v) {
           if (!mbar_wait(&full[stage], phase, g.status, SITE_SK_FULL)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sw = smem_u32(smem + stage * STAGE_BYTES);
@@ -194,13 +223,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int q = warp & 3;
     const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
     int seg = 0;
-    long long u = u_begin;
-    while (u < u_end) {
-      const int tile = (int)(u / g.k_blocks);
-      const long long tile_begin = (long long)tile * g.k_blocks;
-      const long long tile_end = tile_begin + g.k_blocks;
-      const long long seg_end = tile_end < u_end ? tile_end : u_end;
-      const bool whole = (u == tile_begin) && (seg_end == tile_end);
+    int v = 0;
+    while (v < nv) {
+      int tile, kb_first;
+      locate(v, tile, kb_first);
+      const int seg_end = segment_end(v, tile);
+      const long long tile_begin = (long long)tile * kbn;  // in the units of the cut row-blocks (used for those only)
+      const long long tile_end = tile_begin + kbn;
+      const bool whole = kb_first == 0 && seg_end - v == kbn;
       const int buf = seg & 1;
       const uint32_t aphase = (seg >> 1) & 1;
       if (!epi_all(mbar_wait(&acc_full[buf], aphase, g.status, SITE_SK_EPI))) break;
@@ -311,7 +341,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       } else {
         // partial sum: slot 0 for the first row-block of this CTA's run, slot 1 for the last
-        const int slot = (tile == (int)(u_begin / g.k_blocks)) ? 0 : 1;
+        const int slot = (tile == (int)(u_begin / kbn)) ? 0 : 1;
         float* mine = g.partials + ((long long)blockIdx.x * 2 + slot) * (NX * 128);
 #pragma unroll 1
         for (int c0 = 0; c0 <= last_c0; c0 += CH) {
@@ -390,7 +420,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // ticket_bcast may be reused
       }
-      u = seg_end;
+      v = seg_end;
       ++seg;
     }
   }
@@ -406,6 +436,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   }
 }
 
+// Grid size and the split into cut and whole row-blocks (see the file comment).  One CTA per SM, but never runs
+// shorter than 8 units (144 KB of W): below that the partial-sum exchange costs more than the extra CTAs bring
+// (4096 x 512 weights: 10.6 us against 16 with 148 CTAs).  Whole row-blocks per CTA are used when the cut ones are
+// then shared by few CTAs each (at most about four); otherwise every row-block is cut and a CTA's run is one
+// contiguous stretch of units, which keeps a row-block's partial sums to two or three.
+static int plan_runs(SkinnyArgs& a, int num_sms) {
+  const long long all = (long long)a.n_tiles * a.k_blocks;
+  long long grid = num_sms;
+  if (grid > all / kMinRun) grid = all / kMinRun > 0 ? all / kMinRun : 1;
+  const long long q = a.n_tiles / grid, r = a.n_tiles % grid;
+  if (q >= 1 && (r == 0 || r * 4 >= grid)) {
+    a.whole = (int)q;
+    a.split_tiles = (int)r;
+  } else {
+    a.whole = 0;
+    a.split_tiles = a.n_tiles;
+  }
+  a.units = (long long)a.split_tiles * a.k_blocks;
+  return (int)grid;
+}
+
 template <typename OutT, int NX>
 static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUtensorMap& tx, SkinnyArgs a,
                               cudaStream_t stream) {
@@ -414,10 +465,7 @@ static int launch_skinny_inst(moye_b200_ctx* h, const CUtensorMap& tw, const CUt
   constexpr int SMEM = STAGES * STAGE + 512 + 1024;
   auto kern = gemm_skinny_kernel<OutT, NX, STAGES>;
   if (int rc = configure_once(h, kern, (int)SMEM)) return rc;
-  // one CTA per SM, but never runs shorter than 8 units (144 KB of W): below that the partial-sum exchange
-  // costs more than the extra CTAs bring (4096 x 512 weights: 10.6 us against 16 with 148 CTAs)
-  long long grid = h->num_sms;
-  if (grid > a.units / kMinRun) grid = a.units / kMinRun > 0 ? a.units / kMinRun : 1;
+  const int grid = plan_runs(a, h->num_sms);
   // workspace: a fixed ticket area (zero at rest: the kernel restores it, moye_b200_status() clears it after a
   // time-out) then the partial slots.  It is allocated once, sized for the widest X tile, so no launch ever frees
   // or re-allocates it.
@@ -471,7 +519,6 @@ int launch_gemm_skinny(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tens
   a.M = (int)M; a.N = (int)N; a.K = (int)K;
   a.n_tiles = (int)((N + 127) / 128);
   a.k_blocks = (int)((K + 63) / 64);
-  a.units = (long long)a.n_tiles * a.k_blocks;
   const uint32_t fmt = A->dtype == MOYE_BF16 ? 1u : 0u;
   a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(nx >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.alpha = p->alpha * p->scale_a * p->scale_b;
@@ -610,7 +657,6 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   a.M = (int)M; a.N = (int)N; a.K = (int)K;
   a.n_tiles = (int)((N + 127) / 128);
   a.k_blocks = (int)((K + 63) / 64);
-  a.units = (long long)a.n_tiles * a.k_blocks;
   const uint32_t fmt = A->dtype == MOYE_BF16 ? 1u : 0u;
   a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(nx >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   a.alpha = alpha;
@@ -626,8 +672,7 @@ extern "C" int moye_b200_gemm_skinny_static(const moye_tensor_t* D, const moye_t
   // The array keeps whatever the previous call left: the tickets (and the built-in status word)
   // must read zero when the kernel starts, the partial tiles are always written before they are read.
   MOYE_CUDA(cudaMemsetAsync(su->base, 0, kStaticStatusBytes + (size_t)a.n_tiles * sizeof(int), stream));
-  long long grid = su->num_sms;
-  if (grid > a.units / kMinRun) grid = a.units / kMinRun > 0 ? a.units / kMinRun : 1;
+  const int grid = plan_runs(a, su->num_sms);
   if (nx == 16) {
     if (out == MOYE_F32) launch_skinny_static<float, 16>(tw, tx, a, (int)grid, stream);
     else if (out == MOYE_F16) launch_skinny_static<__half, 16>(tw, tx, a, (int)grid, stream);

@@ -413,7 +413,10 @@ def test_config5_decode_skinny(mb, ho, dev):
 
 @pytest.mark.parametrize("M,N,K", [(1, 512, 512), (7, 1000, 2048), (16, 1024, 1024), (17, 640, 8192), (32, 4096, 4096),
                                    (3, 129, 520), (16, 148 * 128, 64), (33, 1000, 2048), (64, 4096, 4096),
-                                   (100, 640, 8192), (128, 148 * 128, 192), (128, 28672, 1024)])
+                                   (100, 640, 8192), (128, 148 * 128, 192), (128, 28672, 1024),
+                                   # more row-blocks than SMs: whole row-blocks per CTA after the cut ones (185 = 148 + 37,
+                                   # 296 = 2 x 148 with nothing cut, 149 = one over, where every row-block is cut instead)
+                                   (16, 185 * 128, 512), (5, 296 * 128 - 40, 512), (16, 149 * 128, 1024)])
 def test_skinny_shapes(mb, ho, dev, M, N, K):
     x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
     ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)
