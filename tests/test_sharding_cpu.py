@@ -61,3 +61,45 @@ def test_two_gloo_ranks_shard_and_gather(tmp_path):
         ok_rows, ok_cols, slowest = open(tmp_path / f"rank{r}.txt").read().split()
         assert ok_rows == "1" and ok_cols == "1"
         assert float(slowest) == 11.0
+
+
+def test_stream_k_schedule_covers_every_unit_once():
+    """The arithmetic of the decode kernel's schedule (`plan_runs` and the `locate` / `segment_end` lambdas of
+    csrc/gemm_skinny.cu), restated here line for line: for T row-blocks of k K-blocks on up to 148 CTAs, every
+    (row-block, K-block) unit is processed exactly once, and no CTA produces more than the two partial pieces its
+    workspace slots hold.  (The kernel itself is checked against the oracle on the same shapes in the GPU tests.)"""
+    def plan(T, kb, sms=148, k_min=8):
+        total = T * kb
+        grid = min(sms, total // k_min) if total // k_min > 0 else 1
+        q, r = T // grid, T % grid
+        whole, split = (q, r) if q >= 1 and (r == 0 or r * 4 >= grid) else (0, T)
+        return grid, whole, split, split * kb
+
+    for T, kb in [(224, 128), (64, 128), (112, 64), (1, 8), (8, 16), (148, 128), (296, 4), (300, 1), (149, 128), (185, 64),
+                  (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8)]:
+        grid, whole, split, units = plan(T, kb)
+        seen = set()
+        for c in range(grid):
+            ub, ue = c * units // grid, (c + 1) * units // grid
+            ns = ue - ub
+            nv = ns + whole * kb
+            v, partial_pieces = 0, 0
+            while v < nv:
+                if v < ns:
+                    u = ub + v
+                    tile = u // kb
+                    k = u - tile * kb
+                    seg_end = min((tile + 1) * kb - ub, ns)
+                else:
+                    j = (v - ns) // kb
+                    tile = split + c + j * grid
+                    k = (v - ns) - j * kb
+                    seg_end = ns + (j + 1) * kb
+                if not (k == 0 and seg_end - v == kb):
+                    partial_pieces += 1
+                for i in range(seg_end - v):
+                    assert (tile, k + i) not in seen
+                    seen.add((tile, k + i))
+                v = seg_end
+            assert partial_pieces <= 2, (T, kb, c)
+        assert seen == {(t, k) for t in range(T) for k in range(kb)}, (T, kb)
