@@ -170,8 +170,13 @@ def is_colmajor(name):
     return "_colmajor" in name
 
 
-def time_launches(torch, fn, steps, warmup, stream):
-    """Average device time of `fn` in ms: CUDA events on the launching stream, sync on both sides."""
+def time_launches(torch, fn, steps, warmup, stream, settle=0.0):
+    """Average device time of `fn` in ms: CUDA events on the launching stream, sync on both sides.  `settle` seconds of idle
+    before the warm-up let the clocks recover when the previous workload ran into the power cap (the `also` workloads are each
+    meant to be timed alone, and a bandwidth-bound kernel timed in the first milliseconds after a 1 kW GEMM measured 5-15 % slow)."""
+    if settle > 0:
+        torch.cuda.synchronize()
+        time.sleep(settle)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -710,7 +715,7 @@ def extras(mb, torch, dev, peaks):
             i[0] += 1
             plans[i[0] % nset](sp)
 
-        ms = time_launches(torch, fn, 20, 5, stream)
+        ms = time_launches(torch, fn, 20, 5, stream, settle=0.5)
         if M <= 512:
             nbytes = (M * K + N * K + M * N) * 2
             out[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"],
@@ -734,7 +739,7 @@ def library_rates(torch, dev, ours):
 
     def run(name, fn, flops):
         try:
-            ms = time_launches(torch, fn, 10, 3, stream)
+            ms = time_launches(torch, fn, 10, 3, stream, settle=0.5)
         except Exception as e:  # a kind this torch build has no library kernel for
             res[name] = {"unavailable": str(e).splitlines()[0][:120]}
             return
@@ -807,7 +812,7 @@ def copy_rates(mb, torch, dev, peaks, steps, warmup):
             i[0] += 1
             plans[i[0] % 4](sp)
 
-        ms = time_launches(torch, fn, steps, warmup, stream)
+        ms = time_launches(torch, fn, steps, warmup, stream, settle=0.5)
         gbs = 2.0 * m * n * 2 / ms / 1e6
         res[label] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
     return res
@@ -832,7 +837,7 @@ def transpose_rates(mb, torch, dev, peaks, steps, warmup):
             i[0] += 1
             plans[i[0] % nset](sp)
 
-        ms = time_launches(torch, fn, steps, warmup, stream)
+        ms = time_launches(torch, fn, steps, warmup, stream, settle=0.5)
         gbs = 2.0 * m * n * srcs[0].element_size() / ms / 1e6
         res[label] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
         del srcs, dsts, plans
