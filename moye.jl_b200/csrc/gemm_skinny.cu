@@ -439,14 +439,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 // Grid size and the split into cut and whole row-blocks (see the file comment).  One CTA per SM, but never runs
 // shorter than 8 units (144 KB of W): below that the partial-sum exchange costs more than the extra CTAs bring
 // (4096 x 512 weights: 10.6 us against 16 with 148 CTAs).  Whole row-blocks per CTA are used when the cut ones are
-// then shared by few CTAs each (at most about four); otherwise every row-block is cut and a CTA's run is one
-// contiguous stretch of units, which keeps a row-block's partial sums to two or three.
+// then shared by few CTAs each (at most about four) and every CTA still gets a run of at least 8 of their units;
+// otherwise every row-block is cut and a CTA's run is one contiguous stretch of units, which keeps a row-block's
+// partial sums to two or three.
 static int plan_runs(SkinnyArgs& a, int num_sms) {
   const long long all = (long long)a.n_tiles * a.k_blocks;
   long long grid = num_sms;
   if (grid > all / kMinRun) grid = all / kMinRun > 0 ? all / kMinRun : 1;
   const long long q = a.n_tiles / grid, r = a.n_tiles % grid;
-  if (q >= 1 && (r == 0 || r * 4 >= grid)) {
+  // every CTA must get a run of the cut row-blocks (the exchange counts on all CTAs between a row-block's first and
+  // last owner arriving), and not a shorter one than kMinRun
+  if (q >= 1 && (r == 0 || (r * 4 >= grid && r * a.k_blocks >= grid * kMinRun))) {
     a.whole = (int)q;
     a.split_tiles = (int)r;
   } else {

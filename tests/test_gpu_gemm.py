@@ -416,7 +416,10 @@ def test_config5_decode_skinny(mb, ho, dev):
                                    (100, 640, 8192), (128, 148 * 128, 192), (128, 28672, 1024),
                                    # more row-blocks than SMs: whole row-blocks per CTA after the cut ones (185 = 148 + 37,
                                    # 296 = 2 x 148 with nothing cut, 149 = one over, where every row-block is cut instead)
-                                   (16, 185 * 128, 512), (5, 296 * 128 - 40, 512), (16, 149 * 128, 1024)])
+                                   (16, 185 * 128, 512), (5, 296 * 128 - 40, 512), (16, 149 * 128, 1024),
+                                   # few, short row-blocks: 17 row-blocks of 2 K blocks on 4 CTAs (one left over: too few
+                                   # units to give every CTA a run of the cut row-block, so every row-block is cut)
+                                   (75, 2064, 128), (16, 185 * 128, 2048)])
 def test_skinny_shapes(mb, ho, dev, M, N, K):
     x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
     ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)

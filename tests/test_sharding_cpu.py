@@ -72,16 +72,19 @@ def test_stream_k_schedule_covers_every_unit_once():
         total = T * kb
         grid = min(sms, total // k_min) if total // k_min > 0 else 1
         q, r = T // grid, T % grid
-        whole, split = (q, r) if q >= 1 and (r == 0 or r * 4 >= grid) else (0, T)
+        whole, split = (q, r) if q >= 1 and (r == 0 or (r * 4 >= grid and r * kb >= grid * k_min)) else (0, T)
         return grid, whole, split, split * kb
 
     for T, kb in [(224, 128), (64, 128), (112, 64), (1, 8), (8, 16), (148, 128), (296, 4), (300, 1), (149, 128), (185, 64),
-                  (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8)]:
+                  (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8), (17, 2), (5, 3), (150, 2), (223, 16)]:
         grid, whole, split, units = plan(T, kb)
         seen = set()
         for c in range(grid):
             ub, ue = c * units // grid, (c + 1) * units // grid
             ns = ue - ub
+            # the partial-sum exchange of a cut row-block counts on EVERY CTA between its first and its last owner
+            # arriving: no CTA may have an empty run of cut units
+            assert split == 0 or ns >= 1, (T, kb, c)
             nv = ns + whole * kb
             v, partial_pieces = 0, 0
             while v < nv:
