@@ -781,3 +781,74 @@ def test_cpp_caller_through_the_c_abi(dev, tmp_path):
     from test_abi import build_c_abi_smoke
     res = subprocess.run([build_c_abi_smoke(tmp_path)], capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "C_ABI_SMOKE_OK" in res.stdout, res.stdout + res.stderr
+
+
+@pytest.mark.parametrize("seed", [3, 11, 12])
+def test_random_shapes_and_paths_against_the_gpu_float64_product(mb, dev, seed):
+    """A secondary cross-check, not the parity definition (that is the oracle, above): a few hundred random shapes,
+    kernels, tile widths, cluster sizes, output types and majors, alpha / beta, each compared with a float64 product
+    computed on the GPU -- the oracle is too slow to sweep that many shapes, and a sweep like this found a stream-K
+    schedule (75 x 2064 x 128: an empty run between the owners of a cut row-block) that no hand-picked shape had hit.
+    s8 must be exact; a refusal (MoyeError) of an unsupported combination is fine, a wrong number is not."""
+    import random
+    rnd = random.Random(seed)
+    ran = 0
+    for case in range(300):
+        kind = rnd.choice(["bf16", "bf16", "f16", "s8"])
+        path = rnd.choice([0, 0, 1, 2, 3, 4, 5, 5, 2])
+        if path == 2:
+            kind = "bf16" if kind == "s8" else kind
+            M = rnd.randint(1, 128)
+            N = rnd.choice([rnd.randint(1, 400) * 8, rnd.randint(140, 330) * 128, rnd.randint(1, 64) * 128 + rnd.randint(0, 15) * 8])
+            K = rnd.choice([64, 128, 512, 520, 1024, 2048, 4096, rnd.randint(8, 512) * 8])
+        else:
+            M = rnd.choice([rnd.randint(1, 700), rnd.randint(1, 2500), 128, 256, 512])
+            N = rnd.randint(1, 300) * 8 if rnd.random() < 0.7 else rnd.randint(1, 40) * 128
+            K = rnd.choice([16, 64, 128, 1024, 2048, rnd.randint(2, 512) * 16])
+        kw = {}
+        if path == 5:
+            kw = {"split_k": rnd.choice([0, 2, 4, 8]), "tile_n": rnd.choice([0, 128, 256])}
+        elif path == 1:
+            kw = {"tile_n": rnd.choice([0, 64, 128, 256])}
+        elif path == 3:
+            kw = {"tile_n": rnd.choice([128, 256])}
+        elif path == 4:
+            kw = {"tail": rnd.choice([True, False])}
+        if kind == "s8":
+            A = torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8)
+            B = torch.randint(-128, 128, (N, K), device=dev, dtype=torch.int8)
+            C = torch.zeros(M, N, device=dev, dtype=torch.int32)
+        else:
+            dt = torch.bfloat16 if kind == "bf16" else torch.float16
+            A = (torch.rand(M, K, device=dev) * 2 - 1).to(dt)
+            B = (torch.rand(N, K, device=dev) * 2 - 1).to(dt)
+            out_dt = rnd.choice([torch.float32, dt])
+            C = torch.zeros(M, N, device=dev, dtype=out_dt)
+            if rnd.random() < 0.3 and path != 2 and (M * C.element_size()) % 16 == 0:
+                C = torch.zeros(N, M, device=dev, dtype=out_dt).t()                     # M-major D
+        ref = A.double() @ B.double().t()
+        alpha = rnd.choice([1.0, 1.0, 0.5]) if kind != "s8" else 1.0
+        beta, Cin = 0.0, None
+        if kind != "s8" and path != 2 and rnd.random() < 0.25:
+            beta = rnd.choice([1.0, -0.5])
+            Cin = (torch.rand(M, N, device=dev) * 2 - 1).to(C.dtype)
+            if C.stride(0) == 1:
+                Cin = Cin.t().contiguous().t()
+            ref = ref + beta / alpha * Cin.double()
+        try:
+            if Cin is not None:
+                mb.gemm_(mb.MoYeArray(C), mb.MoYeArray(A), mb.MoYeArray(B), mb.MoYeArray(Cin), path=path, alpha=alpha, beta=beta, **kw)
+            else:
+                mb.matmul(A, B, C, path=path, alpha=alpha, **kw)
+            mb.synchronize_status(dev)
+        except mb.MoyeError as e:
+            assert e.code in (-1, -2, -3, -4, -5, -9), (case, kind, path, M, N, K, kw, str(e))
+            continue
+        ran += 1
+        what = (case, kind, path, M, N, K, kw, C.dtype, beta, C.stride(0) == 1)
+        if kind == "s8":
+            assert torch.equal(C.double(), ref), what
+        else:
+            err = ((C.double() - alpha * ref).abs().max() / (alpha * ref).abs().max().clamp_min(1e-6)).item()
+            assert err <= (5e-3 if C.dtype == torch.float32 else 2e-2), what + (err,)
+    assert ran >= 250
