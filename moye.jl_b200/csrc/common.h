@@ -24,6 +24,16 @@ const char* get_error();
 int log_level();
 void log_line(const char* fmt, ...);
 
+// Stream-K decode kernel: with slightly fewer 128-row blocks of W than SMs, one whole row-block per CTA on n_tiles
+// CTAs (no partial sums to exchange, the other SMs idle) is faster than cutting every row-block over all SMs, as long
+// as the idle SMs would not have streamed much: measured on 148 SMs, bf16, M = 1 and 16 (us, whole / cut):
+// 14336 x 2048 14.4 / 18.7, 14336 x 4096 23.8 / 25.4-26.5, 16384 x 4096 24.6 / 28.0-29.3, 18432 x 4096 26.3 / 30.3-31.4,
+// 14336 x 5120 28.7 / 31.1-32.6, 16384 x 6144 34.3 / 36.9-38.3, 17920 x 8192 46.1 / 49.8-51.0, but 14336 x 8192
+// 44.2 / 42.8 and 12288 x 4096 23.4 / 23.1-24.3.
+inline bool stream_k_whole_grid(long long n_tiles, long long k_blocks, int num_sms) {
+  return n_tiles < num_sms && n_tiles * 2 >= num_sms && (num_sms - n_tiles) * k_blocks <= 3000;
+}
+
 // MOYE_B200_NO_PDL=1: launch without the programmatic dependent-launch attribute (to compare with and without).
 // Read once per process.
 bool launch_without_pdl();

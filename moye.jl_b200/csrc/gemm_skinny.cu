@@ -446,6 +446,7 @@ static int plan_runs(SkinnyArgs& a, int num_sms) {
   const long long all = (long long)a.n_tiles * a.k_blocks;
   long long grid = num_sms;
   if (grid > all / kMinRun) grid = all / kMinRun > 0 ? all / kMinRun : 1;
+  if (grid == num_sms && stream_k_whole_grid(a.n_tiles, a.k_blocks, num_sms)) grid = a.n_tiles;  // one whole row-block each
   const long long q = a.n_tiles / grid, r = a.n_tiles % grid;
   // every CTA must get a run of the cut row-blocks (the exchange counts on all CTAs between a row-block's first and
   // last owner arriving), and not a shorter one than kMinRun

@@ -213,7 +213,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   bool use_skinny = p.path == 2;
   if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && !a_mn && !b_mn && N >= 128 && K >= 512) {
     const long long nk = (long long)N * K;
-    use_skinny = nk >= (64ll << 20) || (M <= 4 && nk >= (48ll << 20));
+    use_skinny = nk >= (64ll << 20) || (M <= 4 && nk >= (48ll << 20)) ||
+                 stream_k_whole_grid((N + 127) / 128, (K + 63) / 64, h->num_sms);  // one whole row-block per CTA, nothing to exchange
   }
   if (use_skinny) {
     log_line("gemm %lld x %lld x %lld  in %d  -> stream-K decode kernel", (long long)M, (long long)N, (long long)K, A->dtype);

@@ -419,7 +419,9 @@ def test_config5_decode_skinny(mb, ho, dev):
                                    (16, 185 * 128, 512), (5, 296 * 128 - 40, 512), (16, 149 * 128, 1024),
                                    # few, short row-blocks: 17 row-blocks of 2 K blocks on 4 CTAs (one left over: too few
                                    # units to give every CTA a run of the cut row-block, so every row-block is cut)
-                                   (75, 2064, 128), (16, 185 * 128, 2048)])
+                                   (75, 2064, 128), (16, 185 * 128, 2048),
+                                   # slightly fewer row-blocks than SMs: one whole row-block per CTA on fewer CTAs
+                                   (16, 112 * 128, 2048), (3, 140 * 128 - 24, 1024)])
 def test_skinny_shapes(mb, ho, dev, M, N, K):
     x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
     ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)

@@ -71,12 +71,15 @@ def test_stream_k_schedule_covers_every_unit_once():
     def plan(T, kb, sms=148, k_min=8):
         total = T * kb
         grid = min(sms, total // k_min) if total // k_min > 0 else 1
+        if grid == sms and T < sms and 2 * T >= sms and (sms - T) * kb <= 3000:
+            grid = T                                         # one whole row-block per CTA, the other SMs idle
         q, r = T // grid, T % grid
         whole, split = (q, r) if q >= 1 and (r == 0 or (r * 4 >= grid and r * kb >= grid * k_min)) else (0, T)
         return grid, whole, split, split * kb
 
     for T, kb in [(224, 128), (64, 128), (112, 64), (1, 8), (8, 16), (148, 128), (296, 4), (300, 1), (149, 128), (185, 64),
-                  (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8), (17, 2), (5, 3), (150, 2), (223, 16)]:
+                  (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8), (17, 2), (5, 3), (150, 2), (223, 16), (112, 32), (140, 128), (128, 96),
+                  (147, 1000), (74, 8)]:
         grid, whole, split, units = plan(T, kb)
         seen = set()
         for c in range(grid):
