@@ -60,10 +60,16 @@ __device__ __forceinline__ bool epi_all(bool pred) {
   return r != 0;
 }
 
-__device__ __forceinline__ long long run_start(long long c, long long units, int grid) { return c * units / grid; }
+// First unit of CTA c's run of the cut row-blocks' units: equal contiguous runs; with fewer units than CTAs the first
+// `units` CTAs get one unit each (never an empty run BETWEEN two owners of a row-block: the exchange counts on every CTA
+// from a row-block's first owner to its last arriving).
+__device__ __forceinline__ long long run_start(long long c, long long units, int grid) {
+  return units >= grid ? c * units / grid : (c < units ? c : units);
+}
 
 // The CTA whose run contains unit u.
 __device__ __forceinline__ int owner_of(long long u, long long units, int grid) {
+  if (units < grid) return (int)u;
   long long c = u * grid / units;
   while (c + 1 < grid && run_start(c + 1, units, grid) <= u) ++c;
   while (c > 0 && run_start(c, units, grid) > u) --c;
@@ -437,20 +443,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }
 
 // Grid size and the split into cut and whole row-blocks (see the file comment).  One CTA per SM, but never runs
-// shorter than 8 units (144 KB of W): below that the partial-sum exchange costs more than the extra CTAs bring
-// (4096 x 512 weights: 10.6 us against 16 with 148 CTAs).  Whole row-blocks per CTA are used when the cut ones are
-// then shared by few CTAs each (at most about four) and every CTA still gets a run of at least 8 of their units;
-// otherwise every row-block is cut and a CTA's run is one contiguous stretch of units, which keeps a row-block's
-// partial sums to two or three.
+// shorter than 8 units (144 KB of W) when every row-block is cut: below that the partial-sum exchange costs more than
+// the extra CTAs bring (4096 x 512 weights: 10.6 us against 16 with 148 CTAs).  With at least as many row-blocks as
+// CTAs every CTA owns whole row-blocks and the left-over ones are cut over all CTAs; otherwise every row-block is
+// cut and a CTA's run is one contiguous stretch of units.
 static int plan_runs(SkinnyArgs& a, int num_sms) {
   const long long all = (long long)a.n_tiles * a.k_blocks;
   long long grid = num_sms;
   if (grid > all / kMinRun) grid = all / kMinRun > 0 ? all / kMinRun : 1;
   if (grid == num_sms && stream_k_whole_grid(a.n_tiles, a.k_blocks, num_sms)) grid = a.n_tiles;  // one whole row-block each
   const long long q = a.n_tiles / grid, r = a.n_tiles % grid;
-  // every CTA must get a run of the cut row-blocks (the exchange counts on all CTAs between a row-block's first and
-  // last owner arriving), and not a shorter one than kMinRun
-  if (q >= 1 && (r == 0 || (r * 4 >= grid && r * a.k_blocks >= grid * kMinRun))) {
+  // Short runs and many partial sums per cut row-block are fine here: the exchange is hidden behind the whole
+  // row-blocks (20480 x 8192: 55.7-56.9 -> 51.8-52.7 us with 12 cut row-blocks shared by 12-13 CTAs each; 19200 x 8192:
+  // 54.0-55.4 -> 50.2-50.7 with 2 shared by 74 each)
+  if (q >= 1) {
     a.whole = (int)q;
     a.split_tiles = (int)r;
   } else {

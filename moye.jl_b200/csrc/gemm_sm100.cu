@@ -214,7 +214,8 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && !a_mn && !b_mn && N >= 128 && K >= 512) {
     const long long nk = (long long)N * K;
     use_skinny = nk >= (64ll << 20) || (M <= 4 && nk >= (48ll << 20)) ||
-                 stream_k_whole_grid((N + 127) / 128, (K + 63) / 64, h->num_sms);  // one whole row-block per CTA, nothing to exchange
+                 stream_k_whole_grid((N + 127) / 128, (K + 63) / 64, h->num_sms) ||  // one whole row-block per CTA, nothing to exchange
+                 (N + 127) / 128 > h->num_sms;  // more row-blocks than SMs: the dense kernel would run in waves (20480 x 2048: 29.9 us against 20.6)
   }
   if (use_skinny) {
     log_line("gemm %lld x %lld x %lld  in %d  -> stream-K decode kernel", (long long)M, (long long)N, (long long)K, A->dtype);

@@ -415,13 +415,15 @@ def test_config5_decode_skinny(mb, ho, dev):
                                    (3, 129, 520), (16, 148 * 128, 64), (33, 1000, 2048), (64, 4096, 4096),
                                    (100, 640, 8192), (128, 148 * 128, 192), (128, 28672, 1024),
                                    # more row-blocks than SMs: whole row-blocks per CTA after the cut ones (185 = 148 + 37,
-                                   # 296 = 2 x 148 with nothing cut, 149 = one over, where every row-block is cut instead)
+                                   # 296 = 2 x 148 with nothing cut, 149 = one over: 16 units, one each for 16 CTAs)
                                    (16, 185 * 128, 512), (5, 296 * 128 - 40, 512), (16, 149 * 128, 1024),
-                                   # few, short row-blocks: 17 row-blocks of 2 K blocks on 4 CTAs (one left over: too few
-                                   # units to give every CTA a run of the cut row-block, so every row-block is cut)
+                                   # few, short row-blocks: 17 row-blocks of 2 K blocks on 4 CTAs, one left over with two
+                                   # units for two of the CTAs
                                    (75, 2064, 128), (16, 185 * 128, 2048),
                                    # slightly fewer row-blocks than SMs: one whole row-block per CTA on fewer CTAs
-                                   (16, 112 * 128, 2048), (3, 140 * 128 - 24, 1024)])
+                                   (16, 112 * 128, 2048), (3, 140 * 128 - 24, 1024),
+                                   # a few left-over row-blocks cut over all CTAs: 2 shared by 74 CTAs each, 12 by 12-13
+                                   (8, 150 * 128, 4800), (16, 160 * 128, 2048)])
 def test_skinny_shapes(mb, ho, dev, M, N, K):
     x, w, X, W, dt = operands(ho, "bf16", M, N, K, dev, (9, 10))
     ref = ho.gemm_samples(x, w, dt, M, N, K, np.arange(M, dtype=np.int32), threads=NTHREADS)

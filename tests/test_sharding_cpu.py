@@ -74,20 +74,21 @@ def test_stream_k_schedule_covers_every_unit_once():
         if grid == sms and T < sms and 2 * T >= sms and (sms - T) * kb <= 3000:
             grid = T                                         # one whole row-block per CTA, the other SMs idle
         q, r = T // grid, T % grid
-        whole, split = (q, r) if q >= 1 and (r == 0 or (r * 4 >= grid and r * kb >= grid * k_min)) else (0, T)
+        whole, split = (q, r) if q >= 1 else (0, T)
         return grid, whole, split, split * kb
 
     for T, kb in [(224, 128), (64, 128), (112, 64), (1, 8), (8, 16), (148, 128), (296, 4), (300, 1), (149, 128), (185, 64),
                   (185, 8), (221, 32), (4096, 8), (33, 100), (7, 1), (296, 8), (17, 2), (5, 3), (150, 2), (223, 16), (112, 32), (140, 128), (128, 96),
-                  (147, 1000), (74, 8)]:
+                  (147, 1000), (74, 8), (150, 128), (160, 32), (149, 64), (149, 148), (149, 147)]:
         grid, whole, split, units = plan(T, kb)
         seen = set()
         for c in range(grid):
-            ub, ue = c * units // grid, (c + 1) * units // grid
+            run_start = lambda cc: cc * units // grid if units >= grid else min(cc, units)
+            ub, ue = run_start(c), run_start(c + 1)
             ns = ue - ub
             # the partial-sum exchange of a cut row-block counts on EVERY CTA between its first and its last owner
-            # arriving: no CTA may have an empty run of cut units
-            assert split == 0 or ns >= 1, (T, kb, c)
+            # arriving: no CTA before the last one with units may have an empty run
+            assert ns >= 1 or ub == units, (T, kb, c)
             nv = ns + whole * kb
             v, partial_pieces = 0, 0
             while v < nv:
