@@ -205,17 +205,24 @@ int launch_gemm(moye_b200_ctx* h, const moye_tensor_t* D, const moye_tensor_t* A
   if (p.path == 2 && (a_mn || b_mn)) MOYE_FAIL(MOYE_ERR_UNSUPPORTED_LAYOUT, "the skinny path takes K-major operands");
   // Automatic choice for decode shapes, from measurements at M = 1 .. 128 (bf16, weights from 1024 x 4096 to
   // 28672 x 8192).  The stream-K kernel deals equal runs of (row-block, K-block) units to all SMs; it is the fastest
-  // form on large weights, where the other kernels' tile counts do not divide the SMs (16 x 28672 x 8192: 77-79 us
+  // form on large weights, where the other kernels' tile counts do not divide the SMs (16 x 28672 x 8192: 70-73 us
   // against 93 for split-K on clusters and 85 for single CTAs; 8192 x 8192 and 14336 x 4096 weights with 1-4 rows:
   // 30.4 / 28.6 us against 31.1 / 29.7).  On mid-sized weights the cluster split-K kernel (below) is faster at every M
   // (4096 x 4096: 12.5-14.0 us against 16.6-17.1; 8192 x 2048: 13.8 against 16.5-17; 2048 x 8192: 15.9-16.3 against
-  // 16.5-18.6; 4096 x 1024: 8.9 against 12.4), and from 17 rows the stream-K kernel's X tiles and epilogue grow with M.
+  // 16.5-18.6; 4096 x 1024: 8.9 against 12.4), and from 17 rows the stream-K kernel's X tiles and epilogue grow with M
+  // (8192 x 8192, M = 32: 33.2 us against 30.7), unless it streams whole row-blocks (below).
   bool use_skinny = p.path == 2;
-  if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 16 && !a_mn && !b_mn && N >= 128 && K >= 512) {
+  if (p.path == 0 && p.tile_n == 0 && p.beta == 0.f && kind == KIND_F16 && M <= 128 && !a_mn && !b_mn && N >= 128 && K >= 512 &&
+      (size_t)((N + 127) / 128) * sizeof(int) <= kSkinnyTicketBytes) {
     const long long nk = (long long)N * K;
-    use_skinny = nk >= (64ll << 20) || (M <= 4 && nk >= (48ll << 20)) ||
-                 stream_k_whole_grid((N + 127) / 128, (K + 63) / 64, h->num_sms) ||  // one whole row-block per CTA, nothing to exchange
-                 (N + 127) / 128 > h->num_sms;  // more row-blocks than SMs: the dense kernel would run in waves (20480 x 2048: 29.9 us against 20.6)
+    const long long row_blocks = (N + 127) / 128, k_blocks = (K + 63) / 64;
+    // At least as many row-blocks as SMs (every CTA streams whole row-blocks and the exchange of the cut ones is hidden
+    // behind them; the dense kernel would run in waves), or slightly fewer (one whole row-block per CTA, nothing to
+    // exchange): the stream-K kernel up to 128 rows.  M = 17 ... 128, stream-K / dense kernel [cuBLAS]: 20480 x 8192
+    // 56.5-62.4 / 89.3-90.7 us [56.6-66.0], 16384 x 4096 24.9-26.9 / 30.1-31.5 [25.0-27.1], 28672 x 8192 75.3-85.2 /
+    // 79.9-84.7 [75.4-94.6], 37888 x 4096 51.7-55.9 / 54.6-56.7 [55.9-60.0]; 20480 x 2048 with 1-16 rows 17.9-19.5 / 29.9.
+    const bool streams_whole = row_blocks >= h->num_sms || stream_k_whole_grid(row_blocks, k_blocks, h->num_sms);
+    use_skinny = streams_whole || (M <= 16 && nk >= (64ll << 20)) || (M <= 4 && nk >= (48ll << 20));
   }
   if (use_skinny) {
     log_line("gemm %lld x %lld x %lld  in %d  -> stream-K decode kernel", (long long)M, (long long)N, (long long)K, A->dtype);
