@@ -856,3 +856,35 @@ def test_random_shapes_and_paths_against_the_gpu_float64_product(mb, dev, seed):
             err = ((C.double() - alpha * ref).abs().max() / (alpha * ref).abs().max().clamp_min(1e-6)).item()
             assert err <= (5e-3 if C.dtype == torch.float32 else 2e-2), what + (err,)
     assert ran >= 250
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_decode_shapes_around_the_schedule_boundaries(mb, dev, seed):
+    """Same kind of secondary cross-check for the stream-K kernel's schedule rules: row-block counts around the SM
+    count (whole row-blocks per CTA, a few left over, one fewer, slightly fewer on a smaller grid), 1 to 128 rows, short
+    and long K, through the automatic choice and `path = 2`, with bias / relu now and then, against float64 on the GPU."""
+    import random
+    rnd = random.Random(seed)
+    for case in range(200):
+        M = rnd.choice([1, 2, 4, 7, 16, 17, 31, 32, 33, 64, 100, 128])
+        T = rnd.choice([rnd.randint(70, 160), rnd.randint(140, 156), rnd.randint(145, 300), 148, 296, 149, 147, 74, 111, 112])
+        N = T * 128 - rnd.choice([0, 0, 8, 64, 120])
+        K = rnd.choice([512, 520, 576, 1024, 2048, 3000 // 8 * 8, 4096, 64 * rnd.randint(8, 60)])
+        path = rnd.choice([0, 2])
+        dt = rnd.choice([torch.bfloat16, torch.float16])
+        A = (torch.rand(M, K, device=dev) * 2 - 1).to(dt)
+        B = (torch.rand(N, K, device=dev) * 2 - 1).to(dt)
+        C = torch.zeros(M, N, device=dev, dtype=rnd.choice([torch.float32, dt]))
+        kw = {}
+        ref = A.double() @ B.double().t()
+        if rnd.random() < 0.3:
+            which = rnd.choice(["col", "row"])
+            bvec = torch.randn(N if which == "col" else M, device=dev)
+            kw = {"bias": (bvec, which), "activation": rnd.choice([None, "relu"])}
+            ref = ref + (bvec.double()[None, :] if which == "col" else bvec.double()[:, None])
+            if kw["activation"] == "relu":
+                ref = ref.clamp_min(0)
+        mb.gemm_(mb.MoYeArray(C), mb.MoYeArray(A), mb.MoYeArray(B), None, path=path, **kw)
+        mb.synchronize_status(dev)
+        err = ((C.double() - ref).abs().max() / ref.abs().max().clamp_min(1e-6)).item()
+        assert err <= (5e-3 if C.dtype == torch.float32 else 2e-2), (case, M, N, K, path, C.dtype, err)
