@@ -388,8 +388,11 @@ def run_ours(args):
     comm = mb.Communicator(rank, world, dev) if world > 1 else None
     if args.no_e2e:
         return print_kernel_only(args, rank, world, name, kind, M, N, K, ms, ms_max, value, clocks, peaks, peak_src, comm, dist)
-    hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
-    hC = [torch.empty(C.shape, dtype=C.dtype).pin_memory() for _ in range(2)]
+    # pinned host memory is kept to what the step needs: B only where it is copied from (rank 0), one result buffer
+    # (the copies out are ordered on one stream)
+    hA = A.cpu().pin_memory()
+    hB = B.cpu().pin_memory() if rank == 0 else None
+    hC = [torch.empty(C.shape, dtype=C.dtype).pin_memory()] * 2
     e2e_steps = max(2, min(args.steps, 48))  # enough steps to amortise filling and draining the three-stream pipeline
     pipe = mb.HostGemmPipeline(M, N, K, A.dtype, C.dtype, dev, depth=2, comm=comm, **kw)
     for i in range(3):
@@ -411,7 +414,8 @@ def run_ours(args):
     # the same step with its three phases back to back on one stream (no overlap), for reference
     def serial_step():
         A.copy_(hA, non_blocking=True)
-        B.copy_(hB, non_blocking=True)
+        if hB is not None:
+            B.copy_(hB, non_blocking=True)
         plan(stream_ptr)
         hC[0].copy_(C, non_blocking=True)
 
